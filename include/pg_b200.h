@@ -31,7 +31,8 @@ enum {
   PG_EPI_BIAS_GELU = 2, /* C = gelu_tanh(A W^T + b)       SiglipMLP fc1 */
   PG_EPI_BIAS_RES = 3,  /* C = (A W^T + b) + R            out_proj / fc2 / patch-embed+pos */
   PG_EPI_RES = 4,       /* C = (A W^T) + R                o_proj / down_proj */
-  PG_EPI_GEGLU = 5      /* C = gelu_tanh(A Wg^T) * (A Wu^T), W = [Wg; Wu]  GemmaMLP */
+  PG_EPI_GEGLU = 5,     /* C = gelu_tanh(A Wg^T) * (A Wu^T), W = [Wg; Wu]  GemmaMLP */
+  PG_EPI_SWIGLU = 6     /* C = silu(A Wg^T) * (A Wu^T), W = [Wg; Wu]       gated experts */
 };
 
 /* One exchange of the tensor-parallel decoder over NVLink peer memory (csrc/tp_exchange.cuh; SURVEY.md §8e: the
@@ -247,6 +248,69 @@ int pg_tp_keys_push(const unsigned long long* keys, int B, long long v_local, co
  * [B, nkv, T, hd] tensor (modeling_gemma.py:12-36 attribute parity). */
 int pg_kv_gather(void* out, const void* pool, const int32_t* page_table, int pt_stride,
                  int page_size, int B, int T, int nkv, int hd, int dtype, void* stream);
+
+/* ---- ragged token batches (decoder-only models behind the slot scheduler) -----------------------------------------
+ * A step is a flat list of n_tokens tokens.  Token t belongs to the sequence whose pages are row tok_slot[t] of the
+ * page table and sits at position tok_pos[t] of it, so portions of prompts and single decoded tokens of different
+ * sequences share every launch.  The residual stream x is fp32 [n_tokens, D] whatever the model dtype. */
+
+/* x[t] = emb[ids[t]] * emb_scale + pos_emb[positions[t]]  (pos_emb may be NULL).  A bad id or position sets *err_flag
+ * and gives a zero row. */
+int pg_embed_pos(float* x, const int64_t* ids, const int32_t* positions, const void* emb, const void* pos_emb,
+                 int n_tokens, int D, int64_t vocab, int max_pos, float emb_scale, int* err_flag, int dtype,
+                 void* stream);
+
+/* Residual sum + RMS norm in groups.  x[r] += add_a[r] + add_b[r] (model dtype, either may be NULL; written back),
+ * then every one of the `groups` equal consecutive parts of the row is divided by sqrt(mean(part^2) + eps) and the
+ * row is multiplied by w: out (model dtype, packed rows).  out == NULL: only the sum.  rows_idx (device int32, may be
+ * NULL, not together with a sum) picks the input rows.  groups == 1 is the ordinary RMS norm. */
+int pg_group_rmsnorm(void* out, float* x, const void* add_a, int lda, const void* add_b, int ldb, const void* w,
+                     const int32_t* rows_idx, int rows, int D, int groups, float eps, int dtype, void* stream);
+
+/* RMS norm of the query row and of the key row over ALL their columns (q_w / k_w NULL: no norm), then the key and
+ * value rows go to the paged pools ([pages, page_size, k_cols] and [.., v_cols]) at (tok_slot, tok_pos).  proj holds
+ * the fused projection, row stride ld.  k_cols == 0: a layer that attends another layer's cache. */
+int pg_qknorm_append(void* q_out, const void* proj, int ld, int q_col0, int q_cols, int k_col0, int k_cols,
+                     int v_col0, int v_cols, const void* q_w, const void* k_w, float eps, void* k_pool, void* v_pool,
+                     const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
+                     const int32_t* tok_pos, int n_tokens, int dtype, void* stream);
+
+/* Causal attention of every token over its sequence's cache: keys j with 0 <= pos - j < window (window <= 0: all
+ * j <= pos), score = (q . k_j) * scale - slopes[h] * (pos - j) (slopes: device float[n_heads] or NULL), fp32 softmax,
+ * query head h reads key/value head h / (n_heads / n_kv_heads), key width dim, value width vdim; the result is
+ * multiplied by sigmoid(gate) when gate != NULL (same layout as out) and rounded once. */
+int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                        const void* k_pool, const void* v_pool, const int32_t* page_table, int pt_stride,
+                        int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens, int n_heads,
+                        int n_kv_heads, int dim, int vdim, float scale, int window, const float* slopes, int dtype,
+                        void* stream);
+
+/* xIELU: z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2;  (p, q) = pq[0..1] in
+ * the model dtype.  out may alias z. */
+int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, void* stream);
+
+/* ---- mixture of experts ---------------------------------------------------------------------------------------
+ * pg_moe_route: z = h W_router^T in fp32, s = softmax(z) over all n_route outputs, the `top` largest of
+ *   s + correction are chosen (ties: lowest index), topk_w = s * scale (not renormalised).  w_shared_gate != NULL:
+ *   shared_gate[t] = sigmoid(h . w_shared_gate).
+ * pg_moe_sort: the n_pairs = n_tokens * top pairs with index < n_experts are grouped by expert: offsets[n_experts+1],
+ *   sorted_row[pos] = token row of the pair at sorted position pos, pair_pos[pair] = its position or -1 (an index
+ *   >= n_experts is an identity expert: its output is the token's own input).
+ * pg_moe_gemm: out[pos] = A[row_map ? row_map[pos] : pos] W_e^T for offsets[e] <= pos < offsets[e+1]; W is
+ *   [n_experts][N (2N with swiglu)][K]; swiglu: silu(A Wg^T) * (A Wu^T) with W_e = [Wg; Wu].  impl 0 auto, 1 fp32
+ *   FMA kernel, 2 tcgen05 kernel.
+ * pg_moe_combine: x[t] += sum_k topk_w[t,k] * (y[pair_pos[t,k]] or h[t]) + shared_gate[t] * shared_out[t]. */
+int pg_moe_route(int32_t* topk_idx, float* topk_w, float* shared_gate, const void* h, int ldh, const void* w_router,
+                 const void* correction, const void* w_shared_gate, int n_tokens, int D, int n_route, int top,
+                 float scale, int dtype, void* stream);
+int pg_moe_sort(int32_t* offsets, int32_t* sorted_row, int32_t* pair_pos, const int32_t* topk_idx, int n_pairs,
+                int top, int n_experts, void* stream);
+int pg_moe_gemm(void* out, int ldo, const void* A, int lda, const int32_t* row_map, const void* W,
+                const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int swiglu, int impl, int dtype,
+                void* stream);
+int pg_moe_combine(float* x, const void* y, int ldy, const int32_t* pair_pos, const float* topk_w, const void* h,
+                   int ldh, const void* shared_out, int lds, const float* shared_gate, int n_tokens, int D, int top,
+                   int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,209 @@
+// Causal attention over the paged cache for ragged token batches: sliding window, per-head distance bias,
+// grouped key/value heads, separate key and value widths, optional sigmoid output gate.
+//
+// Token t of the step sits at position p = tok_pos[t] of the sequence whose pages are row tok_slot[t] of the page
+// table; its keys are the positions j with 0 <= p - j < window (window <= 0: all j <= p) of that sequence, which the
+// append kernel has written before this launch (the step's own tokens included), so a prompt portion and a single
+// decoded token are the same case.  score = (q . k_j) * scale - slope[h] * (p - j); fp32 scores, softmax weights and
+// accumulation; out = softmax(score) V, times sigmoid(gate) when a gate is given, rounded once to the model dtype.
+//
+// attention_ragged_kernel: one warp per (token, head).  32 keys per iteration, one key per lane for the dot
+// product (the query row lives in shared memory as fp32), running (max, sum) rescaling, then the lanes switch to the
+// value columns and walk the 32 keys with the weights broadcast by shuffles.  Warps of a CTA are the heads of the
+// same token and its neighbours, so the key / value rows they share are served by L1.
+//
+// attention_ragged_split_kernel: decode-sized batches (a handful of tokens): the keys of one (token, head) are split
+// over the warps of a CTA and the partial (max, sum, acc) triples are merged through shared memory.
+#include "common.cuh"
+
+namespace pg {
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ kp, int dim) {
+  constexpr int V = Vec<T>::N;
+  float acc = 0.f;
+  if ((dim % V) == 0 && (reinterpret_cast<uintptr_t>(kp) & 15) == 0) {
+    for (int c = 0; c < dim; c += V) {
+      float f[V];
+      unpack<T>(*reinterpret_cast<const uint4*>(kp + c), f);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc = fmaf(qs[c + i], f[i], acc);
+    }
+  } else {
+    for (int c = 0; c < dim; ++c) acc = fmaf(qs[c], to_f<T>(kp[c]), acc);
+  }
+  return acc;
+}
+
+struct RagAttnParams {
+  void* out; int ld_out;
+  const void* q; int ld_q;
+  const void* gate; int ld_gate;
+  const void* k_pool; const void* v_pool;
+  const int32_t* page_table; int pt_stride; int page_size;
+  const int32_t* tok_slot; const int32_t* tok_pos;
+  int n_tokens, H, G, dim, vdim;
+  float scale; int window;
+  const float* slopes;
+};
+
+// Process keys [lo, hi] (inclusive) of one (token, head) for the calling warp; (m, l, acc) are the running state.
+template <typename T, int DPL>
+__device__ __forceinline__ void attend_range(const RagAttnParams& p, const float* qs, const int32_t* pt_row, int g,
+                                             int pos, float slope, int lo, int hi, float& m, float& l, float* acc) {
+  const int lane = threadIdx.x & 31;
+  const T* kpool = reinterpret_cast<const T*>(p.k_pool);
+  const T* vpool = reinterpret_cast<const T*>(p.v_pool);
+  const int kw = p.G * p.dim, vw = p.G * p.vdim;
+  for (int j0 = lo; j0 <= hi; j0 += 32) {
+    const int j = j0 + lane;
+    const bool valid = j <= hi;
+    float s = -INFINITY;
+    long long row = 0;
+    if (valid) {
+      row = (long long)pt_row[j / p.page_size] * p.page_size + j % p.page_size;
+      s = dot_row<T>(qs, kpool + row * kw + g * p.dim, p.dim) * p.scale - slope * (float)(pos - j);
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);            // m == -inf on the first block: exp(-inf) = 0
+    const float pj = valid ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pj);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+    const int n = min(32, hi - j0 + 1);
+    for (int jj = 0; jj < n; ++jj) {
+      const float w = __shfl_sync(0xffffffffu, pj, jj);
+      const long long r = __shfl_sync(0xffffffffu, row, jj);
+      const T* vp = vpool + r * vw + g * p.vdim;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < p.vdim) acc[i] = fmaf(w, to_f<T>(vp[c]), acc[i]);
+      }
+    }
+    m = m_new;
+  }
+}
+
+template <typename T, int DPL>
+__device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, float l, const float* acc) {
+  const int lane = threadIdx.x & 31;
+  T* o = reinterpret_cast<T*>(p.out) + (size_t)t * p.ld_out + h * p.vdim;
+  const T* gt = p.gate ? reinterpret_cast<const T*>(p.gate) + (size_t)t * p.ld_gate + h * p.vdim : nullptr;
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < p.vdim) {
+      float v = acc[i] * inv;
+      if (gt) v *= 1.f / (1.f + expf(-to_f<T>(gt[c])));
+      o[c] = from_f<T>(v);
+    }
+  }
+}
+
+template <typename T, int DPL>
+__global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)p.n_tokens * p.H) return;
+  const int t = (int)(item / p.H), h = (int)(item % p.H), g = h / (p.H / p.G);
+  float* qs = smem + (size_t)warp * p.dim;
+  const T* qr = reinterpret_cast<const T*>(p.q) + (size_t)t * p.ld_q + h * p.dim;
+  for (int c = lane; c < p.dim; c += 32) qs[c] = to_f<T>(qr[c]);
+  __syncwarp();
+  const int pos = p.tok_pos[t];
+  const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const float slope = p.slopes ? p.slopes[h] : 0.f;
+  float m = -INFINITY, l = 0.f, acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, lo, pos, m, l, acc);
+  store_out<T, DPL>(p, t, h, l, acc);
+}
+
+// One CTA per (token, head); warp w takes the key blocks w, w + warps, ... of the window.
+template <typename T, int DPL>
+__global__ void __launch_bounds__(256) attention_ragged_split_kernel(RagAttnParams p) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t = blockIdx.x / p.H, h = blockIdx.x % p.H, g = h / (p.H / p.G);
+  float* qs = smem;                                    // [dim]
+  float* part = smem + p.dim;                          // [warps][2 + 32 * DPL]
+  const T* qr = reinterpret_cast<const T*>(p.q) + (size_t)t * p.ld_q + h * p.dim;
+  for (int c = threadIdx.x; c < p.dim; c += blockDim.x) qs[c] = to_f<T>(qr[c]);
+  __syncthreads();
+  const int pos = p.tok_pos[t];
+  const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const float slope = p.slopes ? p.slopes[h] : 0.f;
+  float m = -INFINITY, l = 0.f, acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  for (int b0 = lo + 32 * warp; b0 <= pos; b0 += 32 * warps)
+    attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, b0, min(pos, b0 + 31), m, l, acc);
+  float* mine = part + (size_t)warp * (2 + 32 * DPL);
+  if (lane == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) mine[2 + 32 * i + lane] = acc[i];
+  __syncthreads();
+  if (warp != 0) return;
+  float M = -INFINITY;
+  for (int w = 0; w < warps; ++w) M = fmaxf(M, part[(size_t)w * (2 + 32 * DPL)]);
+  float L = 0.f;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  for (int w = 0; w < warps; ++w) {                     // fixed order: the result does not depend on timing
+    const float* pw = part + (size_t)w * (2 + 32 * DPL);
+    if (pw[1] == 0.f) continue;                         // this warp had no keys
+    const float c = expf(pw[0] - M);
+    L += pw[1] * c;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] += pw[2 + 32 * i + lane] * c;
+  }
+  store_out<T, DPL>(p, t, h, L, acc);
+}
+
+template <typename T, int DPL>
+static int launch_ragged(const RagAttnParams& p, cudaStream_t st) {
+  const long long items = (long long)p.n_tokens * p.H;
+  static const int split_max = env_int("PG_RAGGED_SPLIT_MAX_ITEMS", 592);   // below 4 (token, head) pairs per SM
+  if (items <= split_max && (p.window <= 0 || p.window > 64)) {
+    const int warps = 8;
+    const size_t smem = sizeof(float) * (p.dim + (size_t)warps * (2 + 32 * DPL));
+    attention_ragged_split_kernel<T, DPL><<<(unsigned)items, warps * 32, smem, st>>>(p);
+    return check_launch("attention_ragged_split");
+  }
+  const int warps = 8;
+  const size_t smem = sizeof(float) * (size_t)warps * p.dim;
+  attention_ragged_kernel<T, DPL><<<cdiv(items, warps), warps * 32, smem, st>>>(p);
+  return check_launch("attention_ragged");
+}
+
+}  // namespace pg
+
+using namespace pg;
+
+extern "C" int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                   const void* k_pool, const void* v_pool, const int32_t* page_table, int pt_stride,
+                                   int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens,
+                                   int n_heads, int n_kv_heads, int dim, int vdim, float scale, int window,
+                                   const float* slopes, int dtype, void* stream) {
+  if (n_tokens <= 0) return PG_OK;
+  PG_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_ragged: heads %d / kv heads %d",
+             n_heads, n_kv_heads);
+  PG_REQUIRE(dim > 0 && dim <= 512 && vdim > 0 && vdim <= 256, "attention_ragged: dim %d (<= 512), vdim %d (<= 256)", dim, vdim);
+  RagAttnParams p = {out, ld_out, q, ld_q, gate, ld_gate, k_pool, v_pool, page_table, pt_stride, page_size, tok_slot,
+                     tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, slopes};
+  cudaStream_t st = (cudaStream_t)stream;
+  const int dpl = (vdim + 31) / 32;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    if (dpl <= 1) return launch_ragged<T, 1>(p, st);
+    if (dpl <= 2) return launch_ragged<T, 2>(p, st);
+    if (dpl <= 4) return launch_ragged<T, 4>(p, st);
+    return launch_ragged<T, 8>(p, st);
+  });
+  return PG_OK;
+}

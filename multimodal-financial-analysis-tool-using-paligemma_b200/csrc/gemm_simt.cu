@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(SG_THREADS)
 gemm_simt_kernel(void* __restrict__ Cv, const T* __restrict__ A, const T* __restrict__ W,
                  const T* __restrict__ bias, const T* __restrict__ R, int M, int N, int K, int lda, int ldw,
                  int ldc, int ldr, int res_mod, int out_f32) {
-  constexpr bool DUAL = (EPI == PG_EPI_GEGLU);
+  constexpr bool DUAL = (EPI == PG_EPI_GEGLU || EPI == PG_EPI_SWIGLU);
   __shared__ __align__(16) float As[SG_BK][SG_BM + SG_PAD];
   __shared__ __align__(16) float Bs[SG_BK][SG_BN + SG_PAD];
   __shared__ __align__(16) float Us[DUAL ? SG_BK : 1][SG_BN + SG_PAD];
@@ -81,6 +81,7 @@ gemm_simt_kernel(void* __restrict__ Cv, const T* __restrict__ A, const T* __rest
       v = rnd<T>(v);
       if (EPI == PG_EPI_BIAS_GELU) v = rnd<T>(gelu_tanh(v));
       if (EPI == PG_EPI_GEGLU) v = rnd<T>(rnd<T>(gelu_tanh(v)) * rnd<T>(acu[DUAL ? i : 0][j]));
+      if (EPI == PG_EPI_SWIGLU) v = rnd<T>(rnd<T>(v / (1.f + expf(-v))) * rnd<T>(acu[DUAL ? i : 0][j]));
       if (EPI == PG_EPI_BIAS_RES || EPI == PG_EPI_RES) {
         const int rm = res_mod > 0 ? (m % res_mod) : m;
         v = rnd<T>(v + to_f<T>(R[(size_t)rm * ldr + n]));
@@ -106,6 +107,7 @@ static int launch_simt(void* C, const void* A, const void* W, const void* bias, 
     case PG_EPI_BIAS_RES: PG_SG(PG_EPI_BIAS_RES); break;
     case PG_EPI_RES: PG_SG(PG_EPI_RES); break;
     case PG_EPI_GEGLU: PG_SG(PG_EPI_GEGLU); break;
+    case PG_EPI_SWIGLU: PG_SG(PG_EPI_SWIGLU); break;
     default: set_error("gemm: bad epilogue %d", epi); return PG_ERR_INVALID;
   }
 #undef PG_SG

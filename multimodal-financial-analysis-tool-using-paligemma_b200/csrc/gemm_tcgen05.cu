@@ -34,7 +34,7 @@ struct Params {
 template <typename T, int EPI, int BN, int CL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, Params p) {
-  constexpr bool DUAL = (EPI == PG_EPI_GEGLU);
+  constexpr bool DUAL = (EPI == PG_EPI_GEGLU || EPI == PG_EPI_SWIGLU);
   constexpr int NB_TILES = DUAL ? 2 : 1;              // W tiles per stage
   constexpr int NSTAGES = (DUAL || BN > 128) ? 4 : 6;
   constexpr int W_BYTES = BN * BK * 2;
@@ -180,6 +180,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               x = rnd<T>(x);
               if (EPI == PG_EPI_BIAS_GELU) x = rnd<T>(gelu_tanh_fast(x));
               if (EPI == PG_EPI_GEGLU) x = rnd<T>(rnd<T>(gelu_tanh_fast(x)) * rnd<T>(u[DUAL ? j0 + j : 0]));
+              if (EPI == PG_EPI_SWIGLU) x = rnd<T>(rnd<T>(x / (1.f + __expf(-x))) * rnd<T>(u[DUAL ? j0 + j : 0]));
               if (EPI == PG_EPI_BIAS_RES || EPI == PG_EPI_RES) x = rnd<T>(x + rr[j]);
               o[j] = x;
             }
@@ -250,7 +251,7 @@ bool make_map_2d(CUtensorMap* map, const void* base, long long rows, long long c
 
 template <typename T, int EPI, int BN, int CL = 1>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const Params& p, cudaStream_t st) {
-  constexpr bool DUAL = (EPI == PG_EPI_GEGLU);
+  constexpr bool DUAL = (EPI == PG_EPI_GEGLU || EPI == PG_EPI_SWIGLU);
   constexpr int NSTAGES = (DUAL || BN > 128) ? 4 : 6;
   constexpr int STAGE_BYTES = TILE_BYTES + (DUAL ? 2 : 1) * BN * BK * 2;
   const size_t smem = 1024 + (size_t)NSTAGES * STAGE_BYTES + 8 * (2 * NSTAGES + 4) + 16;
@@ -275,7 +276,7 @@ bool gemm_tc_supported(int M, int N, int K, int lda, int ldw, int ldc, int epi, 
   static const int min_m = env_int("PG_TCGEN05_MIN_M", 4);
   if (!enabled || (dtype != PG_BF16 && dtype != PG_F16)) return false;
   if (M < min_m || N % 8 || K % 8 || lda % 8 || ldw % 8 || ldc % (out_f32 ? 4 : 8)) return false;
-  if (epi < PG_EPI_NONE || epi > PG_EPI_GEGLU) return false;
+  if (epi < PG_EPI_NONE || epi > PG_EPI_SWIGLU) return false;
   return tc::encode_fn() != nullptr;
 }
 
@@ -300,6 +301,8 @@ int gemm_tc(void* C, const void* A, const void* W, const void* bias, const void*
   PG_REQUIRE(!R || (((uintptr_t)R % 16) == 0 && ldr % 8 == 0), "gemm_tc: residual must be 16-byte aligned rows");
   PG_REQUIRE(!bias || ((uintptr_t)bias % 16) == 0, "gemm_tc: bias must be 16-byte aligned");
   const bool bf = dtype == PG_BF16;
+  const bool dual = epi == PG_EPI_GEGLU || epi == PG_EPI_SWIGLU;
+  if (epi == PG_EPI_SWIGLU) goto basic;   // the SiLU pairing lives in the persistent single-CTA kernel only
   if (gemm_tc_swap_wanted(M, N, K, epi, out_f32, res_mod))  // a prompt's worth of rows: CTA pairs, weights as the M operand
     return gemm_tc_swap(C, A, W, R, M, N, K, lda, ldw, ldc, ldr, epi, dtype, st);
   if (res_mod == 0 && gemm_tc_skinny_wanted(M, N, K, epi))  // a few dozen token rows: stream the weights (swap-AB)
@@ -311,21 +314,22 @@ int gemm_tc(void* C, const void* A, const void* W, const void* bias, const void*
   }
   if (gemm_tc_2cta_wanted(M, N, K, epi))  // >= 2 waves of 256 x 256 tiles: CTA pairs (cta_group::2)
     return gemm_tc_2cta(C, A, W, bias, R, M, N, K, lda, ldw, ldc, ldr, res_mod, epi, out_f32, dtype, st);
+basic:
   // 64-wide N tiles when 128-wide ones would occupy well under one wave of the 148 SMs
   static const int bn_env = env_int("PG_GEMM_BN", 0);
   // and 256-wide ones (half the A-operand shared-memory traffic per FLOP) when there is work for > 2 waves
   int bn = bn_env ? bn_env : ((cdiv(M, tc::BM) * cdiv(N, 128) < 100) ? 64 : (cdiv(M, tc::BM) * cdiv(N, 256) >= 296 ? 256 : 128));
-  if (epi == PG_EPI_GEGLU && bn == 256) bn = 128;  // gate+up already fill 512 TMEM columns at 128
+  if (dual && bn == 256) bn = 128;  // gate+up already fill 512 TMEM columns at 128
   static const int mcast_env = env_int("PG_GEMM_MCAST", 1);
   const bool mcast = mcast_env && bn == 256;
   CUtensorMap ma, mw;
-  const int w_rows = (epi == PG_EPI_GEGLU) ? 2 * N : N;
+  const int w_rows = dual ? 2 * N : N;
   PG_REQUIRE(tc::make_map_2d(&ma, A, M, K, lda, tc::BM, bf) && tc::make_map_2d(&mw, W, w_rows, K, ldw, mcast ? bn / 2 : bn, bf),
              "gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%d ldw=%d)", M, N, K, lda, ldw);
   tc::Params p = {C, bias, R, M, N, K, ldc, ldr, res_mod, out_f32};
 #define PG_TC(E)                                                                                       \
   if (bn == 64) return bf ? tc::launch<bf16, E, 64>(ma, mw, p, st) : tc::launch<f16, E, 64>(ma, mw, p, st); \
-  if (mcast && E != PG_EPI_GEGLU)                                                                        \
+  if (mcast && E != PG_EPI_GEGLU && E != PG_EPI_SWIGLU)                                                                        \
     return bf ? tc::launch<bf16, (E == PG_EPI_GEGLU ? PG_EPI_NONE : E), 256, 2>(ma, mw, p, st)           \
               : tc::launch<f16, (E == PG_EPI_GEGLU ? PG_EPI_NONE : E), 256, 2>(ma, mw, p, st);           \
   if (bn == 256 && E != PG_EPI_GEGLU)                                                                    \
@@ -339,6 +343,7 @@ int gemm_tc(void* C, const void* A, const void* W, const void* bias, const void*
     case PG_EPI_BIAS_RES: PG_TC(PG_EPI_BIAS_RES);
     case PG_EPI_RES: PG_TC(PG_EPI_RES);
     case PG_EPI_GEGLU: PG_TC(PG_EPI_GEGLU);
+    case PG_EPI_SWIGLU: PG_TC(PG_EPI_SWIGLU);
   }
 #undef PG_TC
   set_error("gemm_tc: bad epilogue %d", epi);

@@ -1,0 +1,163 @@
+// Row kernels for ragged token batches (decoder-only models served through the slot scheduler): every token t of a
+// step carries the page-table row of its sequence (tok_slot[t]) and its position in that sequence (tok_pos[t]), so
+// portions of prompts and single decoded tokens of different sequences run side by side in one launch.
+//
+// The residual stream of these models is fp32 whatever the model dtype: sums into it, norms and their statistics
+// are evaluated in fp32 and only the normalised rows (the GEMM operands) are rounded to the model dtype.
+#include "common.cuh"
+
+namespace pg {
+
+// ------------------------------------------------------------------ token embedding + learned position vector
+template <typename T>
+__global__ void embed_pos_kernel(float* __restrict__ x, const int64_t* __restrict__ ids, const int32_t* __restrict__ pos,
+                                 const T* __restrict__ emb, const T* __restrict__ pos_emb, int D, int64_t vocab,
+                                 int max_pos, float emb_scale, int* err_flag) {
+  const int t = blockIdx.x;
+  const int64_t id = ids[t];
+  const int p = pos ? pos[t] : 0;
+  const bool ok = id >= 0 && id < vocab && (!pos_emb || (p >= 0 && p < max_pos));
+  if (!ok && err_flag && threadIdx.x == 0) *err_flag = 1;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float v = 0.f;
+    if (ok) {
+      v = to_f<T>(emb[(size_t)id * D + c]) * emb_scale;
+      if (pos_emb) v += to_f<T>(pos_emb[(size_t)p * D + c]);
+    }
+    x[(size_t)t * D + c] = v;
+  }
+}
+
+// ------------------------------------------------------------------ residual sum + RMS norm in groups
+// One warp per (row, group).  x[row] += a[row] + b[row] first (either may be absent; the sum is written back), then
+// each of the `groups` equal consecutive parts of the row is divided by its own sqrt(mean(part^2) + eps) and the
+// whole is multiplied by w.  rows_idx (optional) picks the input rows; output rows are packed.
+template <typename T>
+__global__ void group_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ x, const T* __restrict__ a, int lda,
+                                     const T* __restrict__ b, int ldb, const T* __restrict__ w,
+                                     const int32_t* __restrict__ rows_idx, int rows, int D, int groups, float eps) {
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= rows * groups) return;
+  const int r = item / groups, g = item % groups;
+  const int src = rows_idx ? rows_idx[r] : r;
+  const int gs = D / groups;
+  float* xr = x + (size_t)src * D + g * gs;
+  float ss = 0.f;
+  for (int c = lane; c < gs; c += 32) {
+    float v = xr[c];
+    if (a || b) {
+      float add = 0.f;
+      if (a) add += to_f<T>(a[(size_t)src * lda + g * gs + c]);
+      if (b) add += to_f<T>(b[(size_t)src * ldb + g * gs + c]);
+      v += add;
+      xr[c] = v;
+    }
+    ss += v * v;
+  }
+  if (!out) return;
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+  T* o = out + (size_t)r * D + g * gs;
+  for (int c = lane; c < gs; c += 32) o[c] = from_f<T>(xr[c] * inv * to_f<T>(w[g * gs + c]));
+}
+
+// ------------------------------------------------------------------ query / key norm over the whole projection + cache append
+// One CTA per token.  proj row = [.. q (q_cols) .. k (k_cols) .. v (v_cols) ..] at the given column offsets.
+// q_out = q / rms(q) * q_w over ALL q columns at once (not per head); the key row likewise, written with the value
+// row into the paged pools at (tok_slot, tok_pos).  k_cols == 0: a layer that reads another layer's keys and values.
+template <typename T>
+__global__ void qknorm_append_kernel(T* __restrict__ q_out, const T* __restrict__ proj, int ld, int q_col0, int q_cols,
+                                     int k_col0, int k_cols, int v_col0, int v_cols, const T* __restrict__ q_w,
+                                     const T* __restrict__ k_w, float eps, T* __restrict__ k_pool,
+                                     T* __restrict__ v_pool, const int32_t* __restrict__ page_table, int pt_stride,
+                                     int page_size, const int32_t* __restrict__ tok_slot,
+                                     const int32_t* __restrict__ tok_pos) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const T* row = proj + (size_t)t * ld;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < q_cols; c += blockDim.x) { const float v = to_f<T>(row[q_col0 + c]); ss += v * v; }
+  ss = block_sum(ss, red);
+  float inv = q_w ? 1.f / sqrtf(ss / (float)q_cols + eps) : 1.f;
+  for (int c = threadIdx.x; c < q_cols; c += blockDim.x)
+    q_out[(size_t)t * q_cols + c] = from_f<T>(to_f<T>(row[q_col0 + c]) * inv * (q_w ? to_f<T>(q_w[c]) : 1.f));
+  if (k_cols == 0) return;
+  const int p = tok_pos[t];
+  const size_t slot_row = (size_t)page_table[(size_t)tok_slot[t] * pt_stride + p / page_size] * page_size + p % page_size;
+  ss = 0.f;
+  for (int c = threadIdx.x; c < k_cols; c += blockDim.x) { const float v = to_f<T>(row[k_col0 + c]); ss += v * v; }
+  ss = block_sum(ss, red);
+  inv = k_w ? 1.f / sqrtf(ss / (float)k_cols + eps) : 1.f;
+  for (int c = threadIdx.x; c < k_cols; c += blockDim.x)
+    k_pool[slot_row * k_cols + c] = from_f<T>(to_f<T>(row[k_col0 + c]) * inv * (k_w ? to_f<T>(k_w[c]) : 1.f));
+  for (int c = threadIdx.x; c < v_cols; c += blockDim.x) v_pool[slot_row * v_cols + c] = row[v_col0 + c];
+}
+
+// ------------------------------------------------------------------ xIELU activation
+// z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2.  (p, q) = pq[0..1].
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+template <typename T>
+__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __restrict__ pq, long long n) {
+  const float ap = softplus_f(to_f<T>(pq[0])), an = 0.5f + softplus_f(to_f<T>(pq[1]));
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = to_f<T>(z[i]);
+    const float r = v > 0.f ? ap * v * v + 0.5f * v : an * (expm1f(v) - v) + 0.5f * v;
+    out[i] = from_f<T>(r);
+  }
+}
+
+}  // namespace pg
+
+using namespace pg;
+
+extern "C" int pg_embed_pos(float* x, const int64_t* ids, const int32_t* positions, const void* emb,
+                            const void* pos_emb, int n_tokens, int D, int64_t vocab, int max_pos, float emb_scale,
+                            int* err_flag, int dtype, void* stream) {
+  if (n_tokens <= 0) return PG_OK;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    embed_pos_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(x, ids, positions, (const T*)emb, (const T*)pos_emb,
+                                                                   D, vocab, max_pos, emb_scale, err_flag);
+  });
+  return check_launch("embed_pos");
+}
+
+extern "C" int pg_group_rmsnorm(void* out, float* x, const void* add_a, int lda, const void* add_b, int ldb,
+                                const void* w, const int32_t* rows_idx, int rows, int D, int groups, float eps,
+                                int dtype, void* stream) {
+  if (rows <= 0) return PG_OK;
+  PG_REQUIRE(groups >= 1 && D % groups == 0, "group_rmsnorm: D=%d is not a multiple of groups=%d", D, groups);
+  PG_REQUIRE(!out || w, "group_rmsnorm: a normalised output needs a weight");
+  PG_REQUIRE(!rows_idx || (!add_a && !add_b), "group_rmsnorm: the residual sum takes all rows (no row index)");
+  const int warps = 8;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    group_rmsnorm_kernel<T><<<cdiv((long long)rows * groups, warps), warps * 32, 0, (cudaStream_t)stream>>>(
+        (T*)out, x, (const T*)add_a, lda, (const T*)add_b, ldb, (const T*)w, rows_idx, rows, D, groups, eps);
+  });
+  return check_launch("group_rmsnorm");
+}
+
+extern "C" int pg_qknorm_append(void* q_out, const void* proj, int ld, int q_col0, int q_cols, int k_col0, int k_cols,
+                                int v_col0, int v_cols, const void* q_w, const void* k_w, float eps, void* k_pool,
+                                void* v_pool, const int32_t* page_table, int pt_stride, int page_size,
+                                const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens, int dtype, void* stream) {
+  if (n_tokens <= 0) return PG_OK;
+  PG_REQUIRE(k_cols == 0 || (k_pool && v_pool && page_table && tok_slot && tok_pos && page_size > 0),
+             "qknorm_append: a layer with keys of its own needs the pools and the token map");
+  PG_DISPATCH_DTYPE(dtype, T, {
+    qknorm_append_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
+        (T*)q_out, (const T*)proj, ld, q_col0, q_cols, k_col0, k_cols, v_col0, v_cols, (const T*)q_w, (const T*)k_w, eps,
+        (T*)k_pool, (T*)v_pool, page_table, pt_stride, page_size, tok_slot, tok_pos);
+  });
+  return check_launch("qknorm_append");
+}
+
+extern "C" int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, void* stream) {
+  if (n <= 0) return PG_OK;
+  const int blocks = (int)((n + 1023) / 1024 < 148 * 8 ? (n + 1023) / 1024 : 148 * 8);
+  PG_DISPATCH_DTYPE(dtype, T, {
+    xielu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)z, (const T*)pq, n);
+  });
+  return check_launch("xielu");
+}

@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("PG_LIB_PATH") or os.path.join(_HERE, "libpg_b200.so")
 
 PG_F32, PG_BF16, PG_F16 = 0, 1, 2
-EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RES, EPI_RES, EPI_GEGLU = 0, 1, 2, 3, 4, 5
+EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RES, EPI_RES, EPI_GEGLU, EPI_SWIGLU = 0, 1, 2, 3, 4, 5, 6
 MAX_DECODE_BATCH = 8            # rows one launch of the GEMV kernels can take
 # from this batch size on the decode step runs the tensor-core (swap-AB skinny GEMM) path: the GEMV kernels turn
 # ALU-bound as rows are added (batch 8: 4.34 ms/step vs ~2 ms), tools/kernel_sweep.py SWEEP_B=...
@@ -62,6 +62,17 @@ SIGNATURES = {
     "pg_rmsnorm_reduce": [_vp, _vp, _vp, _vp, _i, _i, _f, _vp, _i, _vp],
     "pg_tp_keys_push": [_vp, _i, _ll, _vp, _vp],
     "pg_kv_gather": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    # ragged token batches + mixture of experts
+    "pg_embed_pos": [_vp, _vp, _vp, _vp, _vp, _i, _i, _ll, _i, _f, _vp, _i, _vp],
+    "pg_group_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "pg_qknorm_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
+    "pg_attention_ragged": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp,
+                            _i, _vp],
+    "pg_xielu": [_vp, _vp, _vp, _ll, _i, _vp],
+    "pg_moe_route": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "pg_moe_sort": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "pg_moe_gemm": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_moe_combine": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp],
 }
 _RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll}
 

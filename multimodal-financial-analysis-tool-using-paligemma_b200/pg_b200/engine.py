@@ -23,6 +23,8 @@ import torch
 
 from . import _cabi as cabi
 from ._cabi import exref, ptr
+from .pool import PagePool
+from .registry import register
 from .dist import TP, check_divisible, combine_argmax_keys, shard_batch, shard_rows, shard_text_layer
 
 
@@ -128,7 +130,9 @@ class PagedKV:
         return out
 
 
-class PaliGemmaEngine:
+@register("PaliGemmaForConditionalGeneration",
+          predicate=lambda cfg: "vision_config" in cfg and "text_config" in cfg)
+class PaliGemmaEngine(PagePool):
     """Owns repacked weights + the KV pool and issues the kernel sequences."""
 
     def __init__(self, config, weights: Mapping[str, torch.Tensor], *, device=None, dtype=None,
@@ -174,10 +178,9 @@ class PaliGemmaEngine:
             adopt = (lambda k, v: None if ".vision_model." in k else adopt_outer(k, v)) if adopt_outer else None
         self._repack(weights, adopt)
         # paged KV pool: [L, pages, page_size, nkv*hd] for K and for V
-        self.num_pages = max(8, (kv_pool_tokens + page_size - 1) // page_size)
+        self._init_pool(max(8, (kv_pool_tokens + page_size - 1) // page_size))
         self.k_pool = torch.zeros((d.L, self.num_pages, page_size, d.nkv * d.hd), dtype=self.dtype, device=self.device)
         self.v_pool = torch.zeros_like(self.k_pool)
-        self._free = list(range(self.num_pages - 1, -1, -1))
         # pinned, device-mapped: kernels store to it only when they meet a bad id, the host reads it without a sync
         self.err_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._err_np = self.err_flag.numpy()
@@ -195,6 +198,15 @@ class PaliGemmaEngine:
         self.fabric = self.tp.make_fabric(d.D, self.device)
         if self.fabric is not None and 2 * d.L + 2 > 4096:
             raise ValueError("too many layers for the exchange sequence numbering")
+
+    @classmethod
+    def from_checkpoint(cls, config, tensors, *, device="cuda", dtype=None, **kw):
+        """Registry entry point: HF-layout tensors (tied head allowed) -> engine on `device`."""
+        dev = torch.device(device)
+        if dtype is not None:
+            tensors = {k: v.to(dtype) if v.is_floating_point() else v for k, v in tensors.items()}
+        tensors = {k: v.to(dev) for k, v in tensors.items()}
+        return cls(config, tensors, device=dev, dtype=dtype, **kw)
 
     def kv_pool_bytes(self) -> int:
         return 2 * self.k_pool.numel() * self.k_pool.element_size()
@@ -298,16 +310,6 @@ class PaliGemmaEngine:
         return e * (d.L * per_layer + self.V_l * d.D + d.D)
 
     # ------------------------------------------------------------------ KV pages
-    def _alloc_pages(self, n: int) -> List[int]:
-        if n > len(self._free):
-            raise RuntimeError(f"KV pool exhausted: need {n} pages, {len(self._free)} free "
-                               f"(pool holds {self.num_pages * self.page_size} tokens; raise kv_pool_tokens)")
-        out = [self._free.pop() for _ in range(n)]
-        return out
-
-    def _free_pages(self, pages: List[int]) -> None:
-        self._free.extend(reversed(pages))
-
     def new_kv(self, batch: int) -> PagedKV:
         return PagedKV(self, batch)
 

@@ -238,3 +238,157 @@ class ContinuousBatcher:
             self.kv.retire(slot)
         self.running.clear()
         self.kv.release()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+@dataclass
+class TokenRequest:
+    prompt: List[int]
+    max_new_tokens: int
+    eos_token_id: Optional[int] = None
+    rid: int = -1
+    fed: int = 0                              # prompt tokens already run
+    tokens: List[int] = field(default_factory=list)
+    done: bool = False
+
+
+class RaggedBatcher:
+    """Continuous batching with chunked prefill for engines whose step takes a flat token list
+    (`engine.forward_tokens`: every token carries its page-table row and position).
+
+    The cache manager is the same SlotKV as above: a static page table with one row per slot, pages from the
+    engine's pool, rows and pages handed on to the next sequence when one ends.  A step holds, side by side, one
+    token of every sequence that is decoding and a portion of the prompts that are still being read, up to
+    `token_budget` tokens; the logits of a position do not depend on what else the step holds.
+
+    Two levels: `admit` / `run_entries` / `finish` run given tokens (replaying a recorded schedule, scoring);
+    `submit` / `step` / `run` generate with the framework's sampling kernels on top of them."""
+
+    def __init__(self, engine, slots: int = 4, max_seq_tokens: Optional[int] = None, token_budget: int = 512,
+                 do_sample: bool = False, temperature: float = 0.8, top_p: float = 0.9, seed: int = 0):
+        self.eng = engine
+        self.slots = int(slots)
+        ps = engine.page_size
+        pool_tokens = (engine.num_pages - 1) * ps
+        cap = min(pool_tokens, engine.cfg.max_positions if max_seq_tokens is None else int(max_seq_tokens))
+        self.kv = SlotKV(engine, self.slots, max(cap, ps))
+        self.token_budget = max(1, int(token_budget))
+        self.sample = (float(temperature), float(top_p), int(seed)) if do_sample else None
+        self.slot_of: Dict[object, int] = {}          # sequence key -> slot
+        self.queue: Deque[TokenRequest] = deque()
+        self.running: Dict[int, TokenRequest] = {}    # slot -> request
+        self.finished: Dict[int, TokenRequest] = {}
+        self._next_rid = 0
+        self.steps_run = 0
+
+    # ---- level 1: run given tokens
+    def free_slots(self) -> List[int]:
+        used = set(self.slot_of.values())
+        return [s for s in range(self.slots) if s not in used]
+
+    def admit(self, key) -> int:
+        if key in self.slot_of:
+            raise ValueError(f"sequence {key!r} is live already")
+        free = self.free_slots()
+        if not free:
+            raise RuntimeError(f"all {self.slots} slots are taken")
+        slot = free[0]
+        self.slot_of[key] = slot
+        self.kv.assign(slot, [], 0)
+        return slot
+
+    def length(self, key) -> int:
+        return self.kv.host_len[self.slot_of[key]]
+
+    @torch.no_grad()
+    def run_entries(self, entries, layer_sink=None) -> torch.Tensor:
+        """entries: (key, tokens, want) triples, `want` = indices into `tokens` whose logits are asked for.  All
+        entries form ONE batch.  Returns fp32 logits, one row per wanted place, in entry order."""
+        ids, slots, positions, rows = [], [], [], []
+        for key, toks, want in entries:
+            slot = self.slot_of[key]
+            n0 = self.kv.host_len[slot]
+            self.kv.ensure(slot, n0 + len(toks))
+            base = len(ids)
+            ids.extend(int(t) for t in toks)
+            slots.extend([slot] * len(toks))
+            positions.extend(range(n0, n0 + len(toks)))
+            rows.extend(base + int(i) for i in want)
+            self.kv.host_len[slot] = n0 + len(toks)
+        self.steps_run += 1
+        return self.eng.forward_tokens(self.kv, ids, slots, positions, rows, layer_sink=layer_sink)
+
+    def finish(self, key) -> None:
+        self.kv.retire(self.slot_of.pop(key))
+
+    # ---- level 2: generation
+    def submit(self, prompt, max_new_tokens: int, eos_token_id: Optional[int] = None) -> int:
+        prompt = [int(t) for t in (prompt.flatten().tolist() if isinstance(prompt, torch.Tensor) else prompt)]
+        if not prompt or max_new_tokens < 1:
+            raise ValueError("a request needs a prompt and max_new_tokens >= 1")
+        cap = self.kv.max_pages * self.eng.page_size
+        if len(prompt) + int(max_new_tokens) > min(cap, self.eng.cfg.max_positions):
+            raise ValueError(f"prompt ({len(prompt)}) + max_new_tokens ({max_new_tokens}) exceeds the capacity of "
+                             f"{min(cap, self.eng.cfg.max_positions)} tokens per sequence")
+        r = TokenRequest(prompt, int(max_new_tokens), eos_token_id, self._next_rid)
+        self._next_rid += 1
+        self.queue.append(r)
+        return r.rid
+
+    def _pages_for(self, r: TokenRequest) -> int:
+        ps = self.eng.page_size
+        return (len(r.prompt) + r.max_new_tokens + ps - 1) // ps
+
+    @torch.no_grad()
+    def step(self) -> None:
+        """Admit what fits, run one step (decode tokens first, then prompt portions up to the budget), sample."""
+        from .generate import _pick
+        while self.queue and self.free_slots():
+            r = self.queue[0]
+            owed = sum(self._pages_for(q) - len(self.kv.pages[s]) for s, q in self.running.items())
+            if self._pages_for(r) + owed > len(self.eng._free):
+                if not self.running:
+                    raise RuntimeError("the KV pool cannot hold this request even alone")
+                break
+            self.queue.popleft()
+            self.running[self.admit(("gen", r.rid))] = r
+        if not self.running:
+            return
+        budget, entries, asked = self.token_budget, [], []
+        for slot, r in sorted(self.running.items(), key=lambda kv_: kv_[1].fed < len(kv_[1].prompt)):
+            if r.fed >= len(r.prompt):                     # decoding: its last token, always scheduled
+                entries.append((("gen", r.rid), [r.tokens[-1]], [0]))
+                asked.append(r)
+                budget -= 1
+            elif budget > 0:
+                n = min(budget, len(r.prompt) - r.fed)
+                last = r.fed + n == len(r.prompt)
+                entries.append((("gen", r.rid), r.prompt[r.fed:r.fed + n], [n - 1] if last else []))
+                r.fed += n
+                budget -= n
+                if last:
+                    asked.append(r)
+        logits = self.run_entries(entries)
+        if asked:
+            picked = _pick(self.eng, logits.contiguous(), self.sample, step=self.steps_run & 0x3fffffff).tolist()
+            self.eng.check_errors()
+            for r, tok in zip(asked, picked):
+                r.tokens.append(int(tok))
+                if (r.eos_token_id is not None and tok == r.eos_token_id) or len(r.tokens) >= r.max_new_tokens:
+                    r.done = True
+        for slot, r in list(self.running.items()):
+            if r.done:
+                self.finish(("gen", r.rid))
+                del self.running[slot]
+                self.finished[r.rid] = r
+
+    def run(self) -> Dict[int, TokenRequest]:
+        while self.queue or self.running:
+            self.step()
+        return self.finished
+
+    def close(self) -> None:
+        for key in list(self.slot_of):
+            self.finish(key)
+        self.running.clear()
+        self.kv.release()
