@@ -298,7 +298,8 @@ int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, v
  *   >= n_experts is an identity expert: its output is the token's own input).
  * pg_moe_gemm: out[pos] = A[row_map ? row_map[pos] : pos] W_e^T for offsets[e] <= pos < offsets[e+1]; W is
  *   [n_experts][N (2N with swiglu)][K]; swiglu: silu(A Wg^T) * (A Wu^T) with W_e = [Wg; Wu].  impl 0 auto, 1 fp32
- *   FMA kernel, 2 tcgen05 kernel.
+ *   FMA kernel, 2 tcgen05 kernel (16-bit dtypes, rows already grouped: row_map NULL; its pipeline waits are bounded and
+ *   *err_flag, a device-visible int that may be NULL, becomes 2 if one gives up).
  * pg_moe_combine: x[t] += sum_k topk_w[t,k] * (y[pair_pos[t,k]] or h[t]) + shared_gate[t] * shared_out[t]. */
 int pg_moe_route(int32_t* topk_idx, float* topk_w, float* shared_gate, const void* h, int ldh, const void* w_router,
                  const void* correction, const void* w_shared_gate, int n_tokens, int D, int n_route, int top,
@@ -306,8 +307,11 @@ int pg_moe_route(int32_t* topk_idx, float* topk_w, float* shared_gate, const voi
 int pg_moe_sort(int32_t* offsets, int32_t* sorted_row, int32_t* pair_pos, const int32_t* topk_idx, int n_pairs,
                 int top, int n_experts, void* stream);
 int pg_moe_gemm(void* out, int ldo, const void* A, int lda, const int32_t* row_map, const void* W,
-                const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int swiglu, int impl, int dtype,
-                void* stream);
+                const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int swiglu, int impl, int* err_flag,
+                int dtype, void* stream);
+/* out[r] = a[row_map[r]] for r < *n_rows (n_rows: device int, NULL = all max_rows): packed rows of `cols` elements. */
+int pg_gather_rows(void* out, const void* a, int lda, const int32_t* row_map, const int32_t* n_rows, int max_rows,
+                   int cols, int dtype, void* stream);
 int pg_moe_combine(float* x, const void* y, int ldy, const int32_t* pair_pos, const float* topk_w, const void* h,
                    int ldh, const void* shared_out, int lds, const float* shared_gate, int n_tokens, int D, int top,
                    int dtype, void* stream);

@@ -10,8 +10,15 @@ constexpr int SG_BM = 64, SG_BN = 64, SG_BK = 16, SG_THREADS = 256, SG_PAD = 4;
 
 template <typename T>
 __device__ __forceinline__ void sg_load_tile(float (*s)[SG_BM + SG_PAD], const T* __restrict__ base, int ld,
-                                             int row0, int rows, int k0, int K) {
+                                             int row0, int rows, int k0, int K, bool vec) {
   constexpr int V = Vec<T>::N;
+  if (!vec) {  // rows that are not 16-byte aligned (K or a leading dimension off the vector width): element loads
+    for (int e = threadIdx.x; e < SG_BM * SG_BK; e += SG_THREADS) {
+      const int r = e / SG_BK, kk = e % SG_BK;
+      s[kk][r] = (row0 + r < rows && k0 + kk < K) ? to_f<T>(base[(size_t)(row0 + r) * ld + k0 + kk]) : 0.f;
+    }
+    return;
+  }
   constexpr int VPR = SG_BK / V;  // vectors per tile row
   for (int e = threadIdx.x; e < SG_BM * VPR; e += SG_THREADS) {
     const int r = e / VPR, kv = (e % VPR) * V;
@@ -29,7 +36,7 @@ template <typename T, int EPI>
 __global__ void __launch_bounds__(SG_THREADS)
 gemm_simt_kernel(void* __restrict__ Cv, const T* __restrict__ A, const T* __restrict__ W,
                  const T* __restrict__ bias, const T* __restrict__ R, int M, int N, int K, int lda, int ldw,
-                 int ldc, int ldr, int res_mod, int out_f32) {
+                 int ldc, int ldr, int res_mod, int out_f32, bool vec) {
   constexpr bool DUAL = (EPI == PG_EPI_GEGLU || EPI == PG_EPI_SWIGLU);
   __shared__ __align__(16) float As[SG_BK][SG_BM + SG_PAD];
   __shared__ __align__(16) float Bs[SG_BK][SG_BN + SG_PAD];
@@ -43,9 +50,9 @@ gemm_simt_kernel(void* __restrict__ Cv, const T* __restrict__ A, const T* __rest
     for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; if (DUAL) acu[i][j] = 0.f; }
 
   for (int k0 = 0; k0 < K; k0 += SG_BK) {
-    sg_load_tile<T>(As, A, lda, m0, M, k0, K);
-    sg_load_tile<T>(Bs, W, ldw, n0, N, k0, K);
-    if (DUAL) sg_load_tile<T>(Us, W + (size_t)N * ldw, ldw, n0, N, k0, K);
+    sg_load_tile<T>(As, A, lda, m0, M, k0, K, vec);
+    sg_load_tile<T>(Bs, W, ldw, n0, N, k0, K, vec);
+    if (DUAL) sg_load_tile<T>(Us, W + (size_t)N * ldw, ldw, n0, N, k0, K, vec);
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < SG_BK; ++kk) {
@@ -95,11 +102,11 @@ gemm_simt_kernel(void* __restrict__ Cv, const T* __restrict__ A, const T* __rest
 template <typename T>
 static int launch_simt(void* C, const void* A, const void* W, const void* bias, const void* R, int M, int N,
                        int K, int lda, int ldw, int ldc, int ldr, int res_mod, int epi, int out_f32,
-                       cudaStream_t st) {
+                       bool vec, cudaStream_t st) {
   dim3 grid(cdiv(N, SG_BN), cdiv(M, SG_BM));
 #define PG_SG(E)                                                                                      \
   gemm_simt_kernel<T, E><<<grid, SG_THREADS, 0, st>>>(C, (const T*)A, (const T*)W, (const T*)bias,   \
-                                                      (const T*)R, M, N, K, lda, ldw, ldc, ldr, res_mod, out_f32)
+                                                      (const T*)R, M, N, K, lda, ldw, ldc, ldr, res_mod, out_f32, vec)
   switch (epi) {
     case PG_EPI_NONE: PG_SG(PG_EPI_NONE); break;
     case PG_EPI_BIAS: PG_SG(PG_EPI_BIAS); break;
@@ -119,9 +126,8 @@ int gemm_simt(void* C, const void* A, const void* W, const void* bias, const voi
               cudaStream_t st) {
   PG_DISPATCH_DTYPE(dtype, T, {
     constexpr int V = Vec<T>::N;
-    PG_REQUIRE(K % V == 0 && lda % V == 0 && ldw % V == 0, "gemm: K=%d lda=%d ldw=%d must be multiples of %d",
-               K, lda, ldw, V);
-    return launch_simt<T>(C, A, W, bias, R, M, N, K, lda, ldw, ldc, ldr, res_mod, epi, out_f32, st);
+    const bool vec = K % V == 0 && lda % V == 0 && ldw % V == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
+    return launch_simt<T>(C, A, W, bias, R, M, N, K, lda, ldw, ldc, ldr, res_mod, epi, out_f32, vec, st);
   });
   return PG_OK;
 }

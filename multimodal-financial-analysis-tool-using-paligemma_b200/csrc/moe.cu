@@ -216,9 +216,26 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const T* __restrict__ 
   }
 }
 
+// rows of the grouped order: out[pos] = a[row_map[pos]] (16-byte copies when the rows allow, else elements)
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ a, int lda,
+                                   const int32_t* __restrict__ row_map, const int32_t* __restrict__ n_rows, int cols) {
+  const int r = blockIdx.x;
+  if (n_rows && r >= *n_rows) return;
+  const T* src = a + (size_t)row_map[r] * lda;
+  T* dst = out + (size_t)r * cols;
+  constexpr int V = Vec<T>::N;
+  if (cols % V == 0 && lda % V == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    for (int c = threadIdx.x * V; c < cols; c += blockDim.x * V)
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = src[c];
+  }
+}
+
 int moe_gemm_tc(void* out, int ldo, const void* A, int lda, const int32_t* row_map, const void* W,
                 const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int swiglu, int dtype,
-                cudaStream_t st);
+                int* err_flag, cudaStream_t st);
 bool moe_gemm_tc_supported(int ldo, int lda, const int32_t* row_map, int N, int K, int dtype);
 
 }  // namespace pg
@@ -250,11 +267,11 @@ extern "C" int pg_moe_sort(int32_t* offsets, int32_t* sorted_row, int32_t* pair_
 
 extern "C" int pg_moe_gemm(void* out, int ldo, const void* A, int lda, const int32_t* row_map, const void* W,
                            const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int swiglu, int impl,
-                           int dtype, void* stream) {
+                           int* err_flag, int dtype, void* stream) {
   if (n_pairs <= 0) return PG_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (impl != 1 && moe_gemm_tc_supported(ldo, lda, row_map, N, K, dtype))
-    return moe_gemm_tc(out, ldo, A, lda, row_map, W, offsets, n_pairs, n_experts, N, K, swiglu, dtype, st);
+    return moe_gemm_tc(out, ldo, A, lda, row_map, W, offsets, n_pairs, n_experts, N, K, swiglu, dtype, err_flag, st);
   PG_REQUIRE(impl != 2, "moe_gemm: the tensor-core kernel does not take this problem (N=%d K=%d dtype %d)", N, K, dtype);
   dim3 grid(cdiv(N, MG_BN), cdiv(n_pairs, MG_BM) + n_experts);
   PG_DISPATCH_DTYPE(dtype, T, {
@@ -277,4 +294,13 @@ extern "C" int pg_moe_combine(float* x, const void* y, int ldy, const int32_t* p
                                                                      ldh, (const T*)shared_out, lds, shared_gate, D, top);
   });
   return check_launch("moe_combine");
+}
+
+extern "C" int pg_gather_rows(void* out, const void* a, int lda, const int32_t* row_map, const int32_t* n_rows,
+                              int max_rows, int cols, int dtype, void* stream) {
+  if (max_rows <= 0) return PG_OK;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    gather_rows_kernel<T><<<max_rows, 128, 0, (cudaStream_t)stream>>>((T*)out, (const T*)a, lda, row_map, n_rows, cols);
+  });
+  return check_launch("gather_rows");
 }

@@ -71,7 +71,8 @@ SIGNATURES = {
     "pg_xielu": [_vp, _vp, _vp, _ll, _i, _vp],
     "pg_moe_route": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "pg_moe_sort": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
-    "pg_moe_gemm": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_moe_gemm": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
+    "pg_gather_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "pg_moe_combine": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp],
 }
 _RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll}

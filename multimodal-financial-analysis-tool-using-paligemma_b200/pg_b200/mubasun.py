@@ -142,6 +142,7 @@ class MubasunEngine(PagePool):
         self.gemm_impl = int(os.environ.get("PG_RAGGED_GEMM_IMPL", gemm_impl))
         self.moe_impl = int(os.environ.get("PG_MOE_IMPL", moe_impl))
         self.small_m_gemv = os.environ.get("PG_RAGGED_GEMV", "1") != "0"
+        self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "16"))
         self._repack(weights)
         # +1: the scheduler parks the unused page-table entries on a page of their own
         self._init_pool((int(kv_pool_tokens) + self.page_size - 1) // self.page_size + 1)
@@ -184,9 +185,6 @@ class MubasunEngine(PagePool):
             return t.to(device=self.device, dtype=self.dtype).contiguous()
 
         D = c.width
-        for what, n in (("width", D),):
-            if n % self.vec:
-                raise ValueError(f"{what} {n} must be a multiple of {self.vec} for {self.dtype}")
         if D % c.groups:
             raise ValueError(f"width {D} is not a multiple of norm.groups {c.groups}")
         self.emb, self.pos = W("embed", (c.vocab, D)), W("pos", (c.max_positions, D))
@@ -333,10 +331,19 @@ class MubasunEngine(PagePool):
         rows, pos = self._new(P, dtype=torch.int32), self._new(P, dtype=torch.int32)
         cabi.check(L.pg_moe_sort(ptr(offsets), ptr(rows), ptr(pos), ptr(idx), P, ml.top, E, st), "moe_sort")
         act, y = self._new(P, ml.ff), self._new(P, D)
-        cabi.check(L.pg_moe_gemm(ptr(act), ml.ff, ptr(h), h.stride(0), ptr(rows), ptr(w["gu"]), ptr(offsets), P, E, ml.ff,
-                                 D, 1, self.moe_impl, self.dt, st), "moe_gemm gate/up")
+        # prompt-sized steps: the rows are gathered into expert order once and both GEMMs run on the tensor cores;
+        # a handful of pairs (decode steps) read h through the row map in the fp32-FMA kernel
+        tc = (self.dtype != torch.float32 and self.moe_impl != 1 and P >= self.moe_tc_min_pairs
+              and D % 8 == 0 and ml.ff % 8 == 0)
+        a, row_map, impl = h, rows, 1
+        if tc:
+            a, row_map, impl = self._new(P, D), None, 2
+            cabi.check(L.pg_gather_rows(ptr(a), ptr(h), h.stride(0), ptr(rows), ptr(offsets[E:]), P, D, self.dt, st),
+                       "gather_rows")
+        cabi.check(L.pg_moe_gemm(ptr(act), ml.ff, ptr(a), a.stride(0), ptr(row_map), ptr(w["gu"]), ptr(offsets), P, E,
+                                 ml.ff, D, 1, impl, ptr(self.err_flag), self.dt, st), "moe_gemm gate/up")
         cabi.check(L.pg_moe_gemm(ptr(y), D, ptr(act), ml.ff, None, ptr(w["dn"]), ptr(offsets), P, E, D, ml.ff, 0,
-                                 self.moe_impl, self.dt, st), "moe_gemm down")
+                                 impl, ptr(self.err_flag), self.dt, st), "moe_gemm down")
         so = None
         if ml.shared_ff:
             so = self._linear(self._linear(h, w["s_gu"], cabi.EPI_SWIGLU), w["s_dn"])
@@ -352,7 +359,9 @@ class MubasunEngine(PagePool):
         if sync:
             torch.cuda.current_stream(self.device).synchronize()
         if self._err_np[0] != 0:
-            self._err_np[0] = 0
+            code, self._err_np[0] = int(self._err_np[0]), 0
+            if code == 2:
+                raise RuntimeError("the grouped expert GEMM gave up waiting on its pipeline (its results are invalid)")
             raise RuntimeError("a token id lies outside the vocabulary or a position outside max_positions")
 
     def weight_bytes(self) -> int:
