@@ -659,6 +659,25 @@ def run_ours(args, rank, world, local):
     emit(line)
 
 
+def run_arch(args):
+    """`--arch mubasun`: see pg_b200/arch_bench.py.  One JSON line; `value` is the prefill throughput at the largest
+    size, the rest (decode, per-op rooflines, the Gemma decoder's numbers) rides along."""
+    from pg_b200 import arch_bench
+    torch.cuda.set_device(0)
+    pk = measured_peaks()
+    sizes = [x for x in args.arch_sizes.split(",") if x]
+    with ClockSampler(0) as clk:
+        res = arch_bench.run(sizes, steps=min(args.steps, 16), warmup=args.warmup, peaks=pk)
+    head = res[sizes[-1]]
+    emit({"metric": "mubasun_prefill_tokens_per_s", "value": head["prefill"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
+          "steps": min(args.steps, 16), "warmup": args.warmup, "ms_per_step": head["prefill"]["ms"],
+          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+          "config": {"model": f"Mubasun {sizes[-1]} (random weights)", "global_batch": 1,
+                     "seq_len": head["prefill"]["tokens"], "parallelism": "single GPU",
+                     "l2": "256 MB scratch write between timed steps"},
+          "peaks": pk, "clocks": clk.summary(), "gpu_launches": res.pop("gpu_launches"), "sizes": res})
+
+
 _REAL_STDOUT = None
 
 
@@ -694,9 +713,16 @@ def main():
                     help="N > 1: what `value` measures. tp = ONE sequence, tensor-parallel decoder (strong scaling, the north "
                          "star's sharding); replicas = one independent sequence per GPU (weak scaling, no data-path "
                          "collective).  Both are measured in every N > 1 run; the other one is reported beside the headline.")
+    ap.add_argument("--arch", default=None, choices=["mubasun"],
+                    help="instead of the default workload: prefill / decode throughput of this decoder-only design at "
+                         "real-model layer sizes (random weights) beside the Gemma decoder at equal size, one GPU")
+    ap.add_argument("--arch-sizes", default="w1024,w2048")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     quiet_stdout()
+    if args.arch is not None:
+        run_arch(args)
+        return
     if args.impl == "reference":
         rank = int(os.environ.get("RANK", "0"))
         run_reference(args, rank, int(os.environ.get("WORLD_SIZE", "1")))

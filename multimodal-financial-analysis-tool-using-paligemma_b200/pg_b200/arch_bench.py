@@ -1,0 +1,341 @@
+"""`bench.py --arch mubasun`: prefill and decode throughput of the Mubasun engine at layer sizes that resemble a
+real model's (random weights), beside the framework's Gemma decoder (the text half of the PaliGemma engine) at equal
+width, depth, query width and feed-forward size, with a per-kernel roofline table for both.
+
+Timing: CUDA events on the launching stream, >= 3 warm-up steps, an L2-sized scratch write between timed steps.
+Roofline of an op = max(algorithmic FLOPs / measured bf16 peak, algorithmic bytes / measured copy bandwidth);
+`frac` = that time / measured time (1.0 = on the roofline)."""
+from __future__ import annotations
+
+import json
+import math
+import os
+from typing import Dict, List
+
+import torch
+
+from . import _cabi as cabi
+
+SIZES = {
+    # width, layers, heads x dim (key) / vdim, kv heads, window, dense ff, experts x ff (top), shared ff, vocab
+    "w1024": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, vdim=128, window=512, ff=4096, experts=8, top=2,
+                  expert_ff=1024, shared_ff=1024, vocab=32000),
+    "w2048": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, ff=8192, experts=16, top=2,
+                  expert_ff=2048, shared_ff=2048, vocab=32000),
+}
+MAX_POS = 4096
+
+
+def mubasun_config(s: dict) -> dict:
+    """Layer order: dense, MoE, MoE reading layer 1's cache, dense ... (every branch of the design is on the path)."""
+    layers = []
+    for i in range(s["layers"]):
+        mixer = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"],
+                 "scale": 1.0 / math.sqrt(s["dim"]), "mask": {"size": s["window"]}}
+        if i % 4 == 2:
+            mixer["kv_from"] = i - 1
+        if i % 2 == 0:
+            mlp = {"kind": "dense", "ff": s["ff"]}
+        else:
+            mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]},
+                   "router": {"experts": s["experts"], "identity": 1, "top": s["top"], "scale": 1.0}}
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Mubasun", "vocab": s["vocab"], "width": s["width"], "max_positions": MAX_POS,
+            "norm": {"eps": 1e-6, "groups": 4}, "layers": layers}
+
+
+def random_mubasun_weights(cfg: dict, device, dtype, seed=0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, out = cfg["width"], {}
+
+    def lin(name, o, i, gain=1.0):
+        out[name] = (torch.randn(o, i, generator=g, device=device) * (gain / math.sqrt(i))).to(dtype)
+
+    def vec(name, n, mean=1.0, std=0.1):
+        out[name] = (mean + std * torch.randn(n, generator=g, device=device)).to(dtype)
+
+    out["embed"] = torch.randn(cfg["vocab"], D, generator=g, device=device).to(dtype)
+    out["pos"] = (0.3 * torch.randn(cfg["max_positions"], D, generator=g, device=device)).to(dtype)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        vec(p + "norm1", D)
+        lin(p + "mix.q", H * dim, D)
+        vec(p + "mix.q.norm", H * dim)
+        if "kv_from" not in m:
+            lin(p + "mix.k", G * dim, D)
+            lin(p + "mix.v", G * vdim, D)
+            vec(p + "mix.k.norm", G * dim)
+        lin(p + "mix.g", H * vdim, D)
+        lin(p + "mix.o", D, H * vdim)
+        ml = L["mlp"]
+        if ml["kind"] == "dense":
+            lin(p + "mlp.up", ml["ff"], D)
+            lin(p + "mlp.down", D, ml["ff"])
+            out[p + "mlp.act"] = torch.zeros(2, device=device, dtype=dtype)
+        else:
+            r = ml["router"]
+            for e in range(r["experts"]):
+                lin(f"{p}mlp.e{e}.gate", ml["expert"]["ff"], D)
+                lin(f"{p}mlp.e{e}.up", ml["expert"]["ff"], D)
+                lin(f"{p}mlp.e{e}.down", D, ml["expert"]["ff"])
+            lin(p + "mlp.router", r["experts"] + r["identity"], D, 2.0)
+            vec(p + "mlp.correction", r["experts"] + r["identity"], 0.0, 0.05)
+            for n, (o, i) in (("gate", (ml["shared"]["ff"], D)), ("up", (ml["shared"]["ff"], D)), ("down", (D, ml["shared"]["ff"]))):
+                lin(p + "mlp.shared." + n, o, i)
+            lin(p + "mlp.shared.sg", 1, D)
+    vec("final.norm", D)
+    lin("head", cfg["vocab"], D)
+    return out
+
+
+def gemma_config(s: dict) -> dict:
+    """Gemma decoder of the same width, depth, query width (heads x 256 = Mubasun's heads x 128) and dense
+    feed-forward size; the vision half is the smallest that the engine accepts and is never run."""
+    hd = 256
+    nq = s["heads"] * s["dim"] // hd
+    return {"image_token_index": s["vocab"] - 1, "vocab_size": s["vocab"], "projection_dim": s["width"],
+            "hidden_size": s["width"], "pad_token_id": 0,
+            "vision_config": {"hidden_size": 144, "intermediate_size": 272, "num_hidden_layers": 1, "num_attention_heads": 2,
+                              "num_channels": 3, "image_size": 56, "patch_size": 14, "num_image_tokens": 16},
+            "text_config": {"vocab_size": s["vocab"], "hidden_size": s["width"], "intermediate_size": s["ff"],
+                            "num_hidden_layers": s["layers"], "num_attention_heads": nq,
+                            "num_key_value_heads": max(1, s["kv_heads"] * s["dim"] // hd), "head_dim": hd}}
+
+
+def random_gemma_weights(cfg: dict, device, dtype, seed=0) -> Dict[str, torch.Tensor]:
+    from . import synth
+    g = torch.Generator(device=device).manual_seed(seed)
+    sd = {}
+    for key, shape, kind in synth.state_dict_spec(cfg):
+        t = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * (0.02 if kind != "ln_w" else 0.1)
+        sd[key] = t.to(dtype)
+    return sd
+
+
+class _Timer:
+    def __init__(self, flush_mb=256):
+        self.scratch = torch.empty(flush_mb << 20, dtype=torch.uint8, device="cuda")
+
+    def run(self, fn, steps, warmup, setup=None):
+        """-> list of per-step ms.  `setup` (untimed) runs before every step, then the L2 flush."""
+        out = []
+        for i in range(warmup + steps):
+            if setup:
+                setup()
+            self.scratch.zero_()                      # larger than L2: the step starts cold
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                out.append(e0.elapsed_time(e1))
+        return out
+
+
+def _med(xs: List[float]) -> float:
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
+
+
+# ------------------------------------------------------------------ algorithmic work per op (one prefill of T tokens)
+def mubasun_work(s: dict, cfg: dict, T: int) -> Dict[str, tuple]:
+    """name -> (FLOPs, bytes) summed over the layers that run the op (bf16 operands, fp32 residual stream)."""
+    D, H, G, dim, vdim, W = s["width"], s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"]
+    w: Dict[str, List[float]] = {}
+
+    def add(name, flops, nbytes):
+        a = w.setdefault(name, [0.0, 0.0])
+        a[0] += flops
+        a[1] += nbytes
+
+    keys = sum(min(t + 1, W) for t in range(T))      # (query, key) pairs per head
+    for L in cfg["layers"]:
+        own = "kv_from" not in L["mixer"]
+        nq, nk, nv, ng = H * dim, G * dim if own else 0, G * vdim if own else 0, H * vdim
+        npj = nq + nk + nv + ng
+        add("norm", 0, T * D * (4 + 4 + 2 + 2 + 2))
+        add("proj", 2 * T * D * npj, 2 * (T * D + npj * D + T * npj))
+        add("qknorm_append", 0, 2 * 2 * T * (nq + nk + nv))
+        add("attention", 2 * keys * H * (dim + vdim), 2 * T * (nq + 2 * ng) + 2 * T * G * (dim + vdim))
+        add("o", 2 * T * ng * D, 2 * (T * ng + ng * D + T * D))
+        ml = L["mlp"]
+        if ml["kind"] == "dense":
+            F = ml["ff"]
+            add("dense_up", 2 * T * D * F, 2 * (T * D + D * F + T * F))
+            add("xielu", 0, 2 * 2 * T * F)
+            add("dense_down", 2 * T * D * F, 2 * (T * F + D * F + T * D))
+        else:
+            r, F, S = ml["router"], ml["expert"]["ff"], ml["shared"]["ff"]
+            E, P = r["experts"], T * r["top"]
+            Pe = P * E / (E + r["identity"])           # pairs that reach a real expert, on average
+            add("moe_route", 2 * T * D * (E + r["identity"] + 1), 2 * T * D)
+            add("moe_sort", 0, 4 * 3 * P)
+            add("moe_gather", 0, 2 * 2 * Pe * D)
+            add("moe_gate_up", 2 * Pe * D * 2 * F, 2 * (Pe * D + E * 2 * F * D + Pe * F))
+            add("moe_down", 2 * Pe * F * D, 2 * (Pe * F + E * F * D + Pe * D))
+            add("shared_gate_up", 2 * T * D * 2 * S, 2 * (T * D + 2 * S * D + T * S))
+            add("shared_down", 2 * T * S * D, 2 * (T * S + S * D + T * D))
+            add("moe_combine", 0, 2 * Pe * D + T * D * (2 + 2 + 8))
+    add("head", 2 * D * s["vocab"], 2 * D * s["vocab"])
+    return {k: (v[0], v[1]) for k, v in w.items()}
+
+
+def gemma_work(s: dict, gcfg: dict, T: int) -> Dict[str, tuple]:
+    t = gcfg["text_config"]
+    D, F, nq, nkv, hd, Ln = t["hidden_size"], t["intermediate_size"], t["num_attention_heads"], t["num_key_value_heads"], \
+        t["head_dim"], t["num_hidden_layers"]
+    nqkv = (nq + 2 * nkv) * hd
+    return {
+        "t_norm": (0, Ln * 2 * T * D * 4),
+        "t_qkv": (Ln * 2 * T * D * nqkv, Ln * 2 * (T * D + nqkv * D + T * nqkv)),
+        "t_rope_append": (0, Ln * 2 * 2 * T * nqkv),
+        "t_attention": (Ln * 2 * T * T * nq * 2 * hd, Ln * 2 * (2 * T * nq * hd + 2 * T * nkv * hd)),   # unmasked: T x T
+        "t_o": (Ln * 2 * T * nq * hd * D, Ln * 2 * (T * nq * hd + nq * hd * D + 2 * T * D)),
+        "t_gate_up": (Ln * 2 * T * D * 2 * F, Ln * 2 * (T * D + 2 * F * D + T * F)),
+        "t_down": (Ln * 2 * T * F * D, Ln * 2 * (T * F + F * D + 2 * T * D)),
+    }
+
+
+def _roofline(work: Dict[str, tuple], times_ms: Dict[str, float], peaks: dict) -> Dict[str, dict]:
+    out = {}
+    for name, (flops, nbytes) in work.items():
+        if name not in times_ms or times_ms[name] <= 0:
+            continue
+        ideal = max(flops / (peaks["tc"] * 1e12), nbytes / (peaks["hbm"] * 1e9)) * 1e3
+        out[name] = {"ms": round(times_ms[name], 4), "roofline_ms": round(ideal, 4), "frac": round(ideal / times_ms[name], 3),
+                     "bound": "tensor" if flops / (peaks["tc"] * 1e12) > nbytes / (peaks["hbm"] * 1e9) else "hbm"}
+    return out
+
+
+# pairs (Mubasun op, the like op of the Gemma decoder)
+LIKE = [("norm", "t_norm"), ("proj", "t_qkv"), ("qknorm_append", "t_rope_append"), ("attention", "t_attention"),
+        ("o", "t_o"), ("dense_up", "t_gate_up"), ("dense_down", "t_down"), ("moe_gate_up", "t_gate_up"),
+        ("moe_down", "t_down"), ("shared_gate_up", "t_gate_up"), ("shared_down", "t_down")]
+
+
+@torch.no_grad()
+def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, context=1024, decode_batches=(1, 8)) -> dict:
+    from .engine import PaliGemmaEngine
+    from .mubasun import MubasunEngine
+    dev, dtype = torch.device("cuda:0"), torch.bfloat16
+    timer = _Timer()
+    result = {}
+    launches0 = cabi.launch_count()
+    for name in sizes:
+        s = SIZES[name]
+        row = {"size": s}
+        # ------------------------------------------------ Mubasun
+        cfg = mubasun_config(s)
+        slots = max(decode_batches)
+        eng = MubasunEngine(cfg, random_mubasun_weights(cfg, dev, dtype), device=dev, dtype=dtype,
+                            kv_pool_tokens=(slots + 1) * (max(prefill_tokens, context) + 256))
+        g = torch.Generator().manual_seed(1)
+        prompt = torch.randint(0, s["vocab"], (prefill_tokens,), generator=g).tolist()
+        b = eng.new_batcher(slots=slots + 1, max_seq_tokens=max(prefill_tokens, context) + 256)
+
+        def prefill():
+            b.admit("p")
+            b.run_entries([("p", prompt, [prefill_tokens - 1])])
+
+        def drop():
+            if "p" in b.slot_of:
+                b.finish("p")
+        ms = timer.run(prefill, steps, warmup, setup=drop)
+        drop()
+        row["prefill"] = {"tokens": prefill_tokens, "ms": round(_med(ms), 3), "tok_s": round(prefill_tokens / _med(ms) * 1e3),
+                          "min_ms": round(min(ms), 3), "max_ms": round(max(ms), 3)}
+        eng._op_timing = True                                    # one more prefill, bracketed op by op
+        for _ in range(2):
+            prefill(); drop(); eng.op_times()
+        reps = 3
+        for _ in range(reps):
+            timer.scratch.zero_(); prefill(); drop()
+        times = {k: v / reps for k, v in eng.op_times().items()}
+        eng._op_timing = False
+        row["prefill_ops"] = _roofline(mubasun_work(s, cfg, prefill_tokens), times, peaks)
+        row["decode"] = {}
+        for B in decode_batches:
+            for i in range(B):
+                b.admit(("d", i))
+            ctx = torch.randint(0, s["vocab"], (context,), generator=g).tolist()
+            for i in range(B):
+                b.run_entries([(("d", i), ctx, [])])
+            step_ents = [(("d", i), [7 + i], [0]) for i in range(B)]
+            n_dec = min(steps * 4, 200)
+            ms = timer.run(lambda: b.run_entries(step_ents), n_dec, warmup + 2)
+            row["decode"][f"batch{B}"] = {"context": context, "ms_per_step": round(_med(ms), 4),
+                                          "tok_s": round(B / _med(ms) * 1e3), "graph": eng.graph_max_tokens >= B,
+                                          "weight_stream_ms": round(_decode_bytes(s, cfg, B) / (peaks["hbm"] * 1e9) * 1e3, 4)}
+            for i in range(B):
+                b.finish(("d", i))
+        b.close()
+        del eng, b
+        torch.cuda.empty_cache()
+        # ------------------------------------------------ Gemma decoder at equal size
+        gcfg = gemma_config(s)
+        geng = PaliGemmaEngine(gcfg, random_gemma_weights(gcfg, dev, dtype), device=dev, dtype=dtype,
+                               kv_pool_tokens=(max(decode_batches) + 1) * (max(prefill_tokens, context) + 512))
+        ids = torch.randint(1, s["vocab"] - 2, (1, prefill_tokens), generator=g).to(dev)
+        holder = {}
+
+        def g_prefill():
+            holder["kv"] = geng.new_kv(1)
+            geng.text_forward(ids, None, holder["kv"], logits="last")
+
+        def g_drop():
+            if "kv" in holder:
+                holder.pop("kv").release()
+        ms = timer.run(g_prefill, steps, warmup, setup=g_drop)
+        g_drop()
+        grow = {"prefill": {"tokens": prefill_tokens, "ms": round(_med(ms), 3), "tok_s": round(prefill_tokens / _med(ms) * 1e3)}}
+        geng._op_timing = True
+        for _ in range(2):
+            g_prefill(); g_drop(); geng.op_times()
+        for _ in range(reps):
+            timer.scratch.zero_(); g_prefill(); g_drop()
+        gt = {k: v / reps for k, v in geng.op_times().items()}
+        geng._op_timing = False
+        grow["prefill_ops"] = _roofline(gemma_work(s, gcfg, prefill_tokens), gt, peaks)
+        grow["decode"] = {}
+        for B in decode_batches:
+            kv = geng.new_kv(B)
+            kv.reserve(context + 512)
+            geng.text_forward(torch.randint(1, s["vocab"] - 2, (B, context), generator=g).to(dev), None, kv, logits="last")
+            ds = geng.decode_state(B)
+            ds.bind(kv, torch.full((B,), 5, dtype=torch.int64, device=dev), position=context + 1)
+            n_dec = min(steps * 4, 200)
+            ms = timer.run(lambda: ds.run_steps(kv, 1), n_dec, warmup + 2)
+            grow["decode"][f"batch{B}"] = {"context": context, "ms_per_step": round(_med(ms), 4), "tok_s": round(B / _med(ms) * 1e3)}
+            kv.release()
+        row["gemma_equal_size"] = grow
+        # like-for-like: how far each Mubasun op is from its roofline against the like Gemma op
+        cmpr = {}
+        for a, bname in LIKE:
+            if a in row["prefill_ops"] and bname in grow["prefill_ops"]:
+                fa, fb = row["prefill_ops"][a]["frac"], grow["prefill_ops"][bname]["frac"]
+                cmpr[a] = {"frac": fa, "like": bname, "like_frac": fb, "distance_ratio": round(fb / fa, 2) if fa > 0 else None}
+        row["like_for_like"] = cmpr
+        result[name] = row
+        del geng
+        torch.cuda.empty_cache()
+    result["gpu_launches"] = int(cabi.launch_count() - launches0)
+    return result
+
+
+def _decode_bytes(s: dict, cfg: dict, B: int) -> float:
+    """Weight bytes one decode step of B tokens must stream (experts: at most B * top of them per MoE layer)."""
+    D, n = s["width"], 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        own = "kv_from" not in m
+        n += D * (m["heads"] * m["dim"] + (m["kv_heads"] * (m["dim"] + m["vdim"]) if own else 0) + 2 * m["heads"] * m["vdim"])
+        ml = L["mlp"]
+        if ml["kind"] == "dense":
+            n += 2 * D * ml["ff"]
+        else:
+            r = ml["router"]
+            n += min(r["experts"], B * r["top"]) * 3 * D * ml["expert"]["ff"] + 3 * D * ml["shared"]["ff"] + D * (r["experts"] + 2)
+    n += D * s["vocab"]
+    return 2.0 * n

@@ -487,29 +487,38 @@ class PaliGemmaEngine(PagePool):
             n, qkv, qo = self._new(T, d.D), self._new(T, nqkv), self._new(T, nq * d.hd)
             att, x2, g = self._new(T, nq * d.hd), self._new(T, d.D), self._new(T, self.F_l)
             scale_div = float(math.sqrt(d.hd))
+            tm = self._op_timer
             for li, w in enumerate(self.t_layers):
-                cabi.check(L.pg_rmsnorm(ptr(n), ptr(x), ptr(w["ln1"]), T, d.D, d.eps, self.dt, st), "rmsnorm")
-                self._gemm(qkv, n, w["qkv"])
-                cabi.check(L.pg_rope_append(ptr(qo), ptr(qkv), ptr(self.inv_freq), ptr(pos), ptr(self.k_pool[li]),
-                                            ptr(self.v_pool[li]), ptr(kv.page_table), kv.max_pages, self.page_size,
-                                            ptr(kv.kv_len), B, q, nq, d.nkv, d.hd, d.max_pos, self.dt, st), "rope_append")
-                if self.attn_tc_text and q >= 16:
-                    cabi.check(L.pg_attention_tc(ptr(att), nq * d.hd, ptr(qo), T, nq * d.hd, 0, ptr(self.k_pool[li]),
-                                                 ptr(self.v_pool[li]), self.num_pages * self.page_size, d.nkv * d.hd, 0, 0,
-                                                 d.hd, 0, ptr(kv.page_table), kv.max_pages, self.page_size, ptr(kv.kv_len),
-                                                 0, q, B, q, nq, d.nkv, d.hd, scale_div, 1, self.dt, st),
-                               "attention (tcgen05)")
-                else:
-                    cabi.check(L.pg_attention(ptr(att), nq * d.hd, ptr(qo), nq * d.hd, ptr(self.k_pool[li]),
-                                              ptr(self.v_pool[li]), 0, 0, ptr(kv.page_table), kv.max_pages, self.page_size,
-                                              ptr(kv.kv_len), 0, q, B, q, nq, d.nkv, d.hd, scale_div, 1, self.dt, st),
-                               "attention")
-                self._gemm(x2, att, w["o"], None, x if tp.rank == 0 else None, res_epi)
+                with tm("t_norm"):
+                    cabi.check(L.pg_rmsnorm(ptr(n), ptr(x), ptr(w["ln1"]), T, d.D, d.eps, self.dt, st), "rmsnorm")
+                with tm("t_qkv"):
+                    self._gemm(qkv, n, w["qkv"])
+                with tm("t_rope_append"):
+                    cabi.check(L.pg_rope_append(ptr(qo), ptr(qkv), ptr(self.inv_freq), ptr(pos), ptr(self.k_pool[li]),
+                                                ptr(self.v_pool[li]), ptr(kv.page_table), kv.max_pages, self.page_size,
+                                                ptr(kv.kv_len), B, q, nq, d.nkv, d.hd, d.max_pos, self.dt, st), "rope_append")
+                with tm("t_attention"):
+                    if self.attn_tc_text and q >= 16:
+                        cabi.check(L.pg_attention_tc(ptr(att), nq * d.hd, ptr(qo), T, nq * d.hd, 0, ptr(self.k_pool[li]),
+                                                     ptr(self.v_pool[li]), self.num_pages * self.page_size, d.nkv * d.hd, 0, 0,
+                                                     d.hd, 0, ptr(kv.page_table), kv.max_pages, self.page_size, ptr(kv.kv_len),
+                                                     0, q, B, q, nq, d.nkv, d.hd, scale_div, 1, self.dt, st),
+                                   "attention (tcgen05)")
+                    else:
+                        cabi.check(L.pg_attention(ptr(att), nq * d.hd, ptr(qo), nq * d.hd, ptr(self.k_pool[li]),
+                                                  ptr(self.v_pool[li]), 0, 0, ptr(kv.page_table), kv.max_pages, self.page_size,
+                                                  ptr(kv.kv_len), 0, q, B, q, nq, d.nkv, d.hd, scale_div, 1, self.dt, st),
+                                   "attention")
+                with tm("t_o"):
+                    self._gemm(x2, att, w["o"], None, x if tp.rank == 0 else None, res_epi)
                 if tp.active:
                     yield ("all_reduce", x2)
-                cabi.check(L.pg_rmsnorm(ptr(n), ptr(x2), ptr(w["ln2"]), T, d.D, d.eps, self.dt, st), "rmsnorm")
-                self._gemm(g, n, w["gu"], None, None, cabi.EPI_GEGLU)
-                self._gemm(x, g, w["down"], None, x2 if tp.rank == 0 else None, res_epi)
+                with tm("t_norm"):
+                    cabi.check(L.pg_rmsnorm(ptr(n), ptr(x2), ptr(w["ln2"]), T, d.D, d.eps, self.dt, st), "rmsnorm")
+                with tm("t_gate_up"):
+                    self._gemm(g, n, w["gu"], None, None, cabi.EPI_GEGLU)
+                with tm("t_down"):
+                    self._gemm(x, g, w["down"], None, x2 if tp.rank == 0 else None, res_epi)
                 if tp.active:
                     yield ("all_reduce", x)
             kv.kv_len.add_(q)

@@ -143,6 +143,11 @@ class MubasunEngine(PagePool):
         self.moe_impl = int(os.environ.get("PG_MOE_IMPL", moe_impl))
         self.small_m_gemv = os.environ.get("PG_RAGGED_GEMV", "1") != "0"
         self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "16"))
+        # steps of up to this many tokens (decode steps, short portions) replay a CUDA graph captured per token count
+        self.graph_max_tokens = int(os.environ.get("PG_RAGGED_GRAPH_TOKENS", "16"))
+        self._graphs: Dict[tuple, tuple] = {}
+        self._op_timing = os.environ.get("PG_OP_TIMING", "0") == "1"
+        self._op_events: List[tuple] = []
         self._repack(weights)
         # +1: the scheduler parks the unused page-table entries on a page of their own
         self._init_pool((int(kv_pool_tokens) + self.page_size - 1) // self.page_size + 1)
@@ -259,7 +264,7 @@ class MubasunEngine(PagePool):
         [len(want_rows), vocab] of the listed rows.  `kv` is the scheduler's slot table; its pages for the new
         positions must be reserved (SlotKV.ensure).  layer_sink (debugging): receives the residual stream after
         every layer."""
-        c, L, st = self.cfg, cabi.lib(), cabi.stream()
+        c = self.cfg
         T, nw = len(ids), len(want_rows)
         if T == 0:
             return torch.empty((0, c.vocab), dtype=torch.float32, device=self.device)
@@ -271,7 +276,39 @@ class MubasunEngine(PagePool):
         host[3 * T:4 * T].copy_(torch.as_tensor(positions, dtype=torch.int32))
         if nw:
             host[4 * T:].copy_(torch.as_tensor(want_rows, dtype=torch.int32))
-        dev = host.to(self.device, non_blocking=True)
+        if (T <= self.graph_max_tokens and layer_sink is None and not self._op_timing
+                and not torch.cuda.is_current_stream_capturing()):
+            return self._replay(kv, host, T, nw)
+        return self._forward_device(kv, host.to(self.device, non_blocking=True), T, nw, layer_sink)
+
+    def _replay(self, kv, host: torch.Tensor, T: int, nw: int) -> torch.Tensor:
+        """Small steps are launch-bound (some fifteen launches per layer): the kernel sequence for (T tokens, nw
+        wanted rows) over this slot table is captured once; a step copies its ids / slots / positions into the
+        graph's static input and replays.  Which kernels run depends on the counts only, never on the values."""
+        key = (T, nw, kv.page_table.data_ptr(), kv.max_pages)
+        ent = self._graphs.get(key)
+        if ent is None:
+            static_in = torch.zeros(4 * T + nw, dtype=torch.int32, device=self.device)
+            static_in.copy_(host, non_blocking=True)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):          # warm-up outside the capture (module loading, shared-memory attributes)
+                self._forward_device(kv, static_in, T, nw, None)
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self._forward_device(kv, static_in, T, nw, None)
+            ent = self._graphs[key] = (g, static_in, out)
+            if len(self._graphs) > 64:
+                self._graphs.pop(next(iter(self._graphs)))
+        g, static_in, out = ent
+        static_in.copy_(host, non_blocking=True)
+        g.replay()
+        return out.clone()
+
+    def _forward_device(self, kv, dev: torch.Tensor, T: int, nw: int, layer_sink: Optional[list]) -> torch.Tensor:
+        c, L, st = self.cfg, cabi.lib(), cabi.stream()
+        tm = self._tm
         d_ids, d_slot, d_pos, d_want = dev[:2 * T].view(torch.int64), dev[2 * T:3 * T], dev[3 * T:4 * T], dev[4 * T:]
         D = c.width
         x = self._new(T, D, dtype=torch.float32)
@@ -281,27 +318,35 @@ class MubasunEngine(PagePool):
         pend_a = pend_b = None        # sublayer outputs not yet summed into x (the next norm kernel adds them)
         for li, (lc, w) in enumerate(zip(c.layers, self.layers)):
             m = lc.mixer
-            self._norm(h, x, w["norm"], pend_a, pend_b)
+            with tm("norm"):
+                self._norm(h, x, w["norm"], pend_a, pend_b)
             pend_a = pend_b = None
-            proj = self._linear(h, w["proj"])
+            with tm("proj"):
+                proj = self._linear(h, w["proj"])
             q = self._new(T, w["nq"])
             kp, vp = self.k_pools[w["kv_layer"]], self.v_pools[w["kv_layer"]]
-            cabi.check(L.pg_qknorm_append(ptr(q), ptr(proj), proj.stride(0), w["q_col"], w["nq"], w["k_col"], w["nk"],
-                                          w["v_col"], w["nv"], ptr(w["q_norm"]), ptr(w["k_norm"]), c.eps, ptr(kp), ptr(vp),
-                                          ptr(kv.page_table), kv.max_pages, self.page_size, ptr(d_slot), ptr(d_pos), T,
-                                          self.dt, st), "qknorm_append")
+            with tm("qknorm_append"):
+                cabi.check(L.pg_qknorm_append(ptr(q), ptr(proj), proj.stride(0), w["q_col"], w["nq"], w["k_col"], w["nk"],
+                                              w["v_col"], w["nv"], ptr(w["q_norm"]), ptr(w["k_norm"]), c.eps, ptr(kp),
+                                              ptr(vp), ptr(kv.page_table), kv.max_pages, self.page_size, ptr(d_slot),
+                                              ptr(d_pos), T, self.dt, st), "qknorm_append")
             att = self._new(T, w["ng"])
             gate = proj[:, w["g_col"]:]
-            cabi.check(L.pg_attention_ragged(ptr(att), att.stride(0), ptr(q), q.stride(0), ptr(gate), proj.stride(0),
-                                             ptr(kp), ptr(vp), ptr(kv.page_table), kv.max_pages, self.page_size,
-                                             ptr(d_slot), ptr(d_pos), T, m.heads, m.kv_heads, m.dim, m.vdim, m.scale,
-                                             m.window, ptr(w["slopes"]), self.dt, st), "attention_ragged")
-            pend_a = self._linear(att, w["o"])
+            with tm("attention"):
+                cabi.check(L.pg_attention_ragged(ptr(att), att.stride(0), ptr(q), q.stride(0), ptr(gate), proj.stride(0),
+                                                 ptr(kp), ptr(vp), ptr(kv.page_table), kv.max_pages, self.page_size,
+                                                 ptr(d_slot), ptr(d_pos), T, m.heads, m.kv_heads, m.dim, m.vdim, m.scale,
+                                                 m.window, ptr(w["slopes"]), self.dt, st), "attention_ragged")
+            with tm("o"):
+                pend_a = self._linear(att, w["o"])
             ml = lc.mlp
             if ml is not None and ml.kind == "dense":
-                u = self._linear(h, w["up"])
-                cabi.check(L.pg_xielu(ptr(u), ptr(u), ptr(w["act"]), u.numel(), self.dt, st), "xielu")
-                pend_b = self._linear(u, w["down"])
+                with tm("dense_up"):
+                    u = self._linear(h, w["up"])
+                with tm("xielu"):
+                    cabi.check(L.pg_xielu(ptr(u), ptr(u), ptr(w["act"]), u.numel(), self.dt, st), "xielu")
+                with tm("dense_down"):
+                    pend_b = self._linear(u, w["down"])
             elif ml is not None:
                 self._moe(x, h, ml, w)
             if layer_sink is not None:
@@ -309,27 +354,32 @@ class MubasunEngine(PagePool):
                 pend_a = pend_b = None
                 layer_sink.append(x.clone())
         if pend_a is not None or pend_b is not None:
-            self._norm(None, x, None, pend_a, pend_b)
+            with tm("norm"):
+                self._norm(None, x, None, pend_a, pend_b)
         if nw == 0:
             return torch.empty((0, c.vocab), dtype=torch.float32, device=self.device)
         hf = self._new(nw, D)
-        self._norm(hf, x, self.final_norm, rows_idx=d_want, rows=nw)
-        return self._linear(hf, self.head, out_f32=True)
+        with tm("norm"):
+            self._norm(hf, x, self.final_norm, rows_idx=d_want, rows=nw)
+        with tm("head"):
+            return self._linear(hf, self.head, out_f32=True)
 
     def _moe(self, x, h, ml: MlpCfg, w: dict) -> None:
         """x += sum over the chosen experts (identity experts return h) + gated shared expert."""
-        L, st = cabi.lib(), cabi.stream()
+        L, st, tm = cabi.lib(), cabi.stream(), self._tm
         T, D = h.shape
         P, E = T * ml.top, ml.experts
         idx = self._new(P, dtype=torch.int32)
         wts = self._new(P, dtype=torch.float32)
         sg = self._new(T, dtype=torch.float32) if ml.shared_ff else None
-        cabi.check(L.pg_moe_route(ptr(idx), ptr(wts), ptr(sg), ptr(h), h.stride(0), ptr(w["router"]), ptr(w["correction"]),
-                                  ptr(w.get("s_sg")), T, D, E + ml.identity, ml.top, ml.router_scale, self.dt, st),
-                   "moe_route")
+        with tm("moe_route"):
+            cabi.check(L.pg_moe_route(ptr(idx), ptr(wts), ptr(sg), ptr(h), h.stride(0), ptr(w["router"]),
+                                      ptr(w["correction"]), ptr(w.get("s_sg")), T, D, E + ml.identity, ml.top,
+                                      ml.router_scale, self.dt, st), "moe_route")
         offsets = self._new(E + 1, dtype=torch.int32)
         rows, pos = self._new(P, dtype=torch.int32), self._new(P, dtype=torch.int32)
-        cabi.check(L.pg_moe_sort(ptr(offsets), ptr(rows), ptr(pos), ptr(idx), P, ml.top, E, st), "moe_sort")
+        with tm("moe_sort"):
+            cabi.check(L.pg_moe_sort(ptr(offsets), ptr(rows), ptr(pos), ptr(idx), P, ml.top, E, st), "moe_sort")
         act, y = self._new(P, ml.ff), self._new(P, D)
         # prompt-sized steps: the rows are gathered into expert order once and both GEMMs run on the tensor cores;
         # a handful of pairs (decode steps) read h through the row map in the fp32-FMA kernel
@@ -338,17 +388,43 @@ class MubasunEngine(PagePool):
         a, row_map, impl = h, rows, 1
         if tc:
             a, row_map, impl = self._new(P, D), None, 2
-            cabi.check(L.pg_gather_rows(ptr(a), ptr(h), h.stride(0), ptr(rows), ptr(offsets[E:]), P, D, self.dt, st),
-                       "gather_rows")
-        cabi.check(L.pg_moe_gemm(ptr(act), ml.ff, ptr(a), a.stride(0), ptr(row_map), ptr(w["gu"]), ptr(offsets), P, E,
-                                 ml.ff, D, 1, impl, ptr(self.err_flag), self.dt, st), "moe_gemm gate/up")
-        cabi.check(L.pg_moe_gemm(ptr(y), D, ptr(act), ml.ff, None, ptr(w["dn"]), ptr(offsets), P, E, D, ml.ff, 0,
-                                 impl, ptr(self.err_flag), self.dt, st), "moe_gemm down")
+            with tm("moe_gather"):
+                cabi.check(L.pg_gather_rows(ptr(a), ptr(h), h.stride(0), ptr(rows), ptr(offsets[E:]), P, D, self.dt, st),
+                           "gather_rows")
+        with tm("moe_gate_up"):
+            cabi.check(L.pg_moe_gemm(ptr(act), ml.ff, ptr(a), a.stride(0), ptr(row_map), ptr(w["gu"]), ptr(offsets), P, E,
+                                     ml.ff, D, 1, impl, ptr(self.err_flag), self.dt, st), "moe_gemm gate/up")
+        with tm("moe_down"):
+            cabi.check(L.pg_moe_gemm(ptr(y), D, ptr(act), ml.ff, None, ptr(w["dn"]), ptr(offsets), P, E, D, ml.ff, 0,
+                                     impl, ptr(self.err_flag), self.dt, st), "moe_gemm down")
         so = None
         if ml.shared_ff:
-            so = self._linear(self._linear(h, w["s_gu"], cabi.EPI_SWIGLU), w["s_dn"])
-        cabi.check(L.pg_moe_combine(ptr(x), ptr(y), D, ptr(pos), ptr(wts), ptr(h), h.stride(0), ptr(so),
-                                    0 if so is None else so.stride(0), ptr(sg), T, D, ml.top, self.dt, st), "moe_combine")
+            with tm("shared_gate_up"):
+                sa = self._linear(h, w["s_gu"], cabi.EPI_SWIGLU)
+            with tm("shared_down"):
+                so = self._linear(sa, w["s_dn"])
+        with tm("moe_combine"):
+            cabi.check(L.pg_moe_combine(ptr(x), ptr(y), D, ptr(pos), ptr(wts), ptr(h), h.stride(0), ptr(so),
+                                        0 if so is None else so.stride(0), ptr(sg), T, D, ml.top, self.dt, st),
+                       "moe_combine")
+
+    # ------------------------------------------------------------------ per-op timing (diagnostic: PG_OP_TIMING=1)
+    def _tm(self, name):
+        """CUDA-event bracket around one op when op timing is on (durations inside the real step, with the L2 state
+        of the real step); `op_times()` sums them per name.  A no-op otherwise."""
+        from .engine import PaliGemmaEngine
+        if not self._op_timing:
+            return PaliGemmaEngine._NoTimer()
+        return PaliGemmaEngine._EvTimer(self._op_events, name)
+
+    def op_times(self, reset: bool = True) -> Dict[str, float]:
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        for name, e0, e1 in self._op_events:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        if reset:
+            self._op_events = []
+        return out
 
     # ------------------------------------------------------------------ serving glue
     def new_batcher(self, **kw):
