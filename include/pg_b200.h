@@ -285,6 +285,19 @@ int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_q, const vo
                         int n_kv_heads, int dim, int vdim, float scale, int window, const float* slopes, int dtype,
                         void* stream);
 
+/* The same attention on the tcgen05 tensor cores for prompt portions (16-bit dtypes, dim and vdim multiples of 64 up
+ * to 256, page_size 64; pg_attention_ragged_tc_ok tells).  `tiles` (device int32 [n_tiles][4]) cuts the step's tokens
+ * into runs of up to 128 consecutive tokens of one sequence at consecutive positions: {first token row, rows,
+ * page-table row, position of the first row}; every token of the step must lie in exactly one tile.  pool_rows =
+ * pages * page_size.  Softmax weights are computed in fp32 and rounded to the model dtype as the operand of P V.
+ * Its pipeline waits are bounded; *err_flag (device-visible int, may be NULL) becomes 2 if one gives up. */
+int pg_attention_ragged_tc_ok(int dim, int vdim, int page_size, int ld_q, int ld_out, int ld_gate, int dtype);
+int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                           const void* k_pool, const void* v_pool, long long pool_rows, const int32_t* page_table,
+                           int pt_stride, int page_size, const int32_t* tiles, int n_tiles, int n_tokens, int n_heads,
+                           int n_kv_heads, int dim, int vdim, float scale, int window, const float* slopes,
+                           int* err_flag, int dtype, void* stream);
+
 /* xIELU: z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2;  (p, q) = pq[0..1] in
  * the model dtype.  out may alias z. */
 int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, void* stream);

@@ -30,7 +30,7 @@ struct MoeParams {
 // a barrier would never complete.  The first wait that runs out sets the CTA's flag; every later wait returns at
 // once, the roles leave their loops, the CTA lets its copies in flight land, frees its TMEM and returns, and the
 // host finds the error flag.
-constexpr uint32_t MG_WAIT_LIMIT = 1u << 24;
+constexpr uint32_t MG_WAIT_LIMIT = 1u << 22;
 __device__ __forceinline__ bool mbar_wait_lim(uint32_t bar, uint32_t parity, volatile int* fail) {
   for (uint32_t it = 0; it < MG_WAIT_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;

@@ -145,10 +145,17 @@ class MubasunEngine(PagePool):
         self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "16"))
         # steps of up to this many tokens (decode steps, short portions) replay a CUDA graph captured per token count
         self.graph_max_tokens = int(os.environ.get("PG_RAGGED_GRAPH_TOKENS", "16"))
+        # steps of at least this many tokens run the tcgen05 attention kernel (layers whose head sizes it takes)
+        self.attn_tc_min_tokens = int(os.environ.get("PG_RAGGED_ATTN_TC_MIN", "48"))
         self._graphs: Dict[tuple, tuple] = {}
         self._op_timing = os.environ.get("PG_OP_TIMING", "0") == "1"
         self._op_events: List[tuple] = []
         self._repack(weights)
+        for w, lc in zip(self.layers, self.cfg.layers):
+            npj = w["proj"].shape[0]
+            w["attn_tc"] = bool(cabi.lib().pg_attention_ragged_tc_ok(lc.mixer.dim, lc.mixer.vdim, self.page_size, w["nq"],
+                                                                     w["ng"], npj, self.dt)) and w["g_col"] % 8 == 0
+        self._attn_tc_any = any(w["attn_tc"] for w in self.layers)
         # +1: the scheduler parks the unused page-table entries on a page of their own
         self._init_pool((int(kv_pool_tokens) + self.page_size - 1) // self.page_size + 1)
         self.k_pools: Dict[int, torch.Tensor] = {}
@@ -270,12 +277,25 @@ class MubasunEngine(PagePool):
             return torch.empty((0, c.vocab), dtype=torch.float32, device=self.device)
         if max(positions) >= c.max_positions:
             raise ValueError(f"position {max(positions)} exceeds max_positions {c.max_positions}")
-        host = torch.empty(4 * T + nw, dtype=torch.int32).pin_memory()   # ids (int64) | slot | pos | want
+        # query tiles of the tensor-core attention: runs of <= 128 consecutive tokens of one sequence
+        tiles: List[int] = []
+        if T >= self.attn_tc_min_tokens and self._attn_tc_any:
+            t0 = 0
+            while t0 < T:
+                t1 = t0 + 1
+                while t1 < T and t1 - t0 < 128 and slots[t1] == slots[t0] and positions[t1] == positions[t1 - 1] + 1:
+                    t1 += 1
+                tiles += [t0, t1 - t0, int(slots[t0]), int(positions[t0])]
+                t0 = t1
+        nt = len(tiles) // 4
+        host = torch.empty(4 * T + nw + 4 * nt, dtype=torch.int32).pin_memory()   # ids (int64) | slot | pos | want | tiles
+        if nt:
+            host[4 * T + nw:].copy_(torch.as_tensor(tiles, dtype=torch.int32))
         host[:2 * T].view(torch.int64).copy_(torch.as_tensor(ids, dtype=torch.int64))
         host[2 * T:3 * T].copy_(torch.as_tensor(slots, dtype=torch.int32))
         host[3 * T:4 * T].copy_(torch.as_tensor(positions, dtype=torch.int32))
         if nw:
-            host[4 * T:].copy_(torch.as_tensor(want_rows, dtype=torch.int32))
+            host[4 * T:4 * T + nw].copy_(torch.as_tensor(want_rows, dtype=torch.int32))
         if (T <= self.graph_max_tokens and layer_sink is None and not self._op_timing
                 and not torch.cuda.is_current_stream_capturing()):
             return self._replay(kv, host, T, nw)
@@ -309,7 +329,8 @@ class MubasunEngine(PagePool):
     def _forward_device(self, kv, dev: torch.Tensor, T: int, nw: int, layer_sink: Optional[list]) -> torch.Tensor:
         c, L, st = self.cfg, cabi.lib(), cabi.stream()
         tm = self._tm
-        d_ids, d_slot, d_pos, d_want = dev[:2 * T].view(torch.int64), dev[2 * T:3 * T], dev[3 * T:4 * T], dev[4 * T:]
+        d_ids, d_slot, d_pos, d_want = dev[:2 * T].view(torch.int64), dev[2 * T:3 * T], dev[3 * T:4 * T], dev[4 * T:4 * T + nw]
+        d_tiles, n_qt = dev[4 * T + nw:], (dev.numel() - 4 * T - nw) // 4
         D = c.width
         x = self._new(T, D, dtype=torch.float32)
         cabi.check(L.pg_embed_pos(ptr(x), ptr(d_ids), ptr(d_pos), ptr(self.emb), ptr(self.pos), T, D, c.vocab,
@@ -333,10 +354,19 @@ class MubasunEngine(PagePool):
             att = self._new(T, w["ng"])
             gate = proj[:, w["g_col"]:]
             with tm("attention"):
-                cabi.check(L.pg_attention_ragged(ptr(att), att.stride(0), ptr(q), q.stride(0), ptr(gate), proj.stride(0),
-                                                 ptr(kp), ptr(vp), ptr(kv.page_table), kv.max_pages, self.page_size,
-                                                 ptr(d_slot), ptr(d_pos), T, m.heads, m.kv_heads, m.dim, m.vdim, m.scale,
-                                                 m.window, ptr(w["slopes"]), self.dt, st), "attention_ragged")
+                if n_qt and w["attn_tc"]:
+                    cabi.check(L.pg_attention_ragged_tc(ptr(att), att.stride(0), ptr(q), q.stride(0), ptr(gate),
+                                                        proj.stride(0), ptr(kp), ptr(vp), self.num_pages * self.page_size,
+                                                        ptr(kv.page_table), kv.max_pages, self.page_size, ptr(d_tiles), n_qt,
+                                                        T, m.heads, m.kv_heads, m.dim, m.vdim, m.scale, m.window,
+                                                        ptr(w["slopes"]), ptr(self.err_flag), self.dt, st),
+                               "attention_ragged_tc")
+                else:
+                    cabi.check(L.pg_attention_ragged(ptr(att), att.stride(0), ptr(q), q.stride(0), ptr(gate),
+                                                     proj.stride(0), ptr(kp), ptr(vp), ptr(kv.page_table), kv.max_pages,
+                                                     self.page_size, ptr(d_slot), ptr(d_pos), T, m.heads, m.kv_heads, m.dim,
+                                                     m.vdim, m.scale, m.window, ptr(w["slopes"]), self.dt, st),
+                               "attention_ragged")
             with tm("o"):
                 pend_a = self._linear(att, w["o"])
             ml = lc.mlp

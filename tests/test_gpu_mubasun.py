@@ -65,6 +65,9 @@ CONFIGS = {
         O.layer(O.attn(heads=2, kv_heads=2, dim=24, vdim=8, window=70), O.moe(experts=9, identity=0, top=2, ff=8, shared=0)),
         O.layer(O.attn(heads=6, kv_heads=1, dim=8, vdim=24, window=5, kv_from=0), O.dense(16)),
         O.layer(O.attn(heads=2, kv_heads=2, dim=24, vdim=8, window=1, kv_from=1), None)]),
+    "wide_heads": O.make_config(width=64, groups=2, vocab=72, max_positions=512, layers=[   # the tensor-core attention's sizes
+        O.layer(O.attn(heads=2, kv_heads=1, dim=64, vdim=128, window=100, scale=0.12), O.dense(32)),
+        O.layer(O.attn(heads=2, kv_heads=1, dim=64, vdim=128, window=0, scale=0.12, kv_from=0), O.moe(experts=4, top=2, ff=16))]),
     "odd_head_dim": O.make_config(width=56, groups=7, vocab=64, layers=[
         O.layer(O.attn(heads=3, kv_heads=3, dim=12, vdim=20, window=40, scale=1.0), O.moe(experts=2, identity=1, top=1, ff=32, shared=8)),
         O.layer(O.attn(heads=8, kv_heads=2, dim=4, vdim=36, window=3), O.dense(24))]),
@@ -155,6 +158,56 @@ def test_attention_decode_sized_batches(n_queries):
     out, want = _attention_case(4, 2, 16, 16, 150, 0.2, [299, 150, 64][:n_queries], 300)
     _rows_close(out, want, 2e-5)
     out, want = _attention_case(4, 2, 16, 16, 0, 0.2, [299, 150, 64][:n_queries], 300, dtype=torch.bfloat16)
+    _rows_close(out, want, 2e-2)
+
+
+def _tc_attention_case(H, G, dim, vdim, window, segments, seed=4):
+    """segments: (start position, count) runs of one sequence each (slot = run index + 1, own shuffled pages)."""
+    cabi, L, st = _lib()
+    g = torch.Generator().manual_seed(seed)
+    ps, dtype = 64, torch.bfloat16
+    n = sum(c for _, c in segments)
+    q = torch.randn(n, H * dim, generator=g).to(dtype)
+    gate = torch.randn(n, H * vdim, generator=g).to(dtype)
+    max_len = max(s0 + c for s0, c in segments)
+    pages_per = (max_len + ps - 1) // ps
+    n_pages = pages_per * len(segments) + 2
+    perm = torch.randperm(n_pages, generator=g)
+    kp, vp = torch.zeros(n_pages, ps, G * dim, dtype=dtype), torch.zeros(n_pages, ps, G * vdim, dtype=dtype)
+    table = torch.zeros(len(segments) + 1, pages_per, dtype=torch.int32)
+    tiles, want, row = [], [], 0
+    for si, (s0, c) in enumerate(segments):
+        kc = torch.randn(s0 + c, G * dim, generator=g).to(dtype)
+        vc = torch.randn(s0 + c, G * vdim, generator=g).to(dtype)
+        pg = perm[si * pages_per:(si + 1) * pages_per]
+        table[si + 1] = pg.to(torch.int32)
+        for j in range(s0 + c):
+            kp[pg[j // ps], j % ps], vp[pg[j // ps], j % ps] = kc[j], vc[j]
+        pos = list(range(s0, s0 + c))
+        want.append(O.window_attention(q[row:row + c].to(F64), kc.to(F64), vc.to(F64), pos, H, G, dim, vdim, 0.11, window))
+        for a in range(0, c, 128):
+            tiles += [row + a, min(128, c - a), si + 1, s0 + a]
+        row += c
+    want = torch.cat(want) * torch.sigmoid(gate.to(F64))
+    out = torch.zeros(n, H * vdim, dtype=dtype, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    d = [_dev(t) for t in (q, gate, kp, vp, table, torch.tensor(tiles, dtype=torch.int32),
+                           torch.tensor(O.head_slopes(H), dtype=torch.float32))]
+    assert L.pg_attention_ragged_tc_ok(dim, vdim, ps, H * dim, H * vdim, H * vdim, cabi.PG_BF16)
+    cabi.check(L.pg_attention_ragged_tc(out.data_ptr(), H * vdim, d[0].data_ptr(), H * dim, d[1].data_ptr(), H * vdim,
+                                        d[2].data_ptr(), d[3].data_ptr(), n_pages * ps, d[4].data_ptr(), pages_per, ps,
+                                        d[5].data_ptr(), len(tiles) // 4, n, H, G, dim, vdim, 0.11, window, d[6].data_ptr(),
+                                        err.data_ptr(), cabi.PG_BF16, st))
+    assert int(err) == 0
+    return out, want
+
+
+@pytest.mark.parametrize("H,G,dim,vdim", [(2, 1, 64, 64), (4, 2, 128, 64), (2, 2, 64, 192), (1, 1, 256, 256)])
+@pytest.mark.parametrize("window", [0, 1, 64, 65, 130, 700])
+def test_tensor_core_attention_windows_tiles_and_portions(H, G, dim, vdim, window):
+    """Whole prompts (several query tiles), a portion that starts in the middle of a page and of a window, a portion
+    of two tokens, a single decoded token, all in one launch."""
+    out, want = _tc_attention_case(H, G, dim, vdim, window, [(0, 300), (190, 135), (63, 2), (500, 1), (0, 1)])
     _rows_close(out, want, 2e-2)
 
 
@@ -267,7 +320,7 @@ def test_prompt_logits_and_layer_streams(name, dtype):
     cfg = CONFIGS[name]
     eng, orc = _engine(cfg, seed=11, dtype=dtype)
     b = eng.new_batcher(slots=2)
-    toks = _tokens(90, cfg["vocab"], 1)
+    toks = _tokens(200 if name == "wide_heads" else 90, cfg["vocab"], 1)
     b.admit("a")
     sink = []
     got = b.run_entries([("a", toks, list(range(len(toks))))], layer_sink=sink)
