@@ -672,8 +672,8 @@ def run_arch(args):
     emit({"metric": "mubasun_prefill_tokens_per_s", "value": head["prefill"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
           "steps": min(args.steps, 16), "warmup": args.warmup, "ms_per_step": head["prefill"]["ms"],
           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-          "config": {"model": f"Mubasun {sizes[-1]} (random weights)", "global_batch": 1,
-                     "seq_len": head["prefill"]["tokens"], "parallelism": "single GPU",
+          "config": {"model": f"Mubasun {sizes[-1]} (random weights)", "global_batch": head["prefill"]["sequences"],
+                     "seq_len": head["prefill"]["tokens"] // head["prefill"]["sequences"], "parallelism": "single GPU",
                      "l2": "256 MB scratch write between timed steps"},
           "peaks": pk, "clocks": clk.summary(), "gpu_launches": res.pop("gpu_launches"), "sizes": res})
 

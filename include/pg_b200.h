@@ -278,12 +278,13 @@ int pg_qknorm_append(void* q_out, const void* proj, int ld, int q_col0, int q_co
 /* Causal attention of every token over its sequence's cache: keys j with 0 <= pos - j < window (window <= 0: all
  * j <= pos), score = (q . k_j) * scale - slopes[h] * (pos - j) (slopes: device float[n_heads] or NULL), fp32 softmax,
  * query head h reads key/value head h / (n_heads / n_kv_heads), key width dim, value width vdim; the result is
- * multiplied by sigmoid(gate) when gate != NULL (same layout as out) and rounded once. */
+ * multiplied by sigmoid(gate) when gate != NULL (same layout as out) and rounded once.  ws (fp32 scratch of ws_floats
+ * floats, may be NULL): decode-sized steps split the keys of a token over several CTAs and merge through it. */
 int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
                         const void* k_pool, const void* v_pool, const int32_t* page_table, int pt_stride,
                         int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens, int n_heads,
-                        int n_kv_heads, int dim, int vdim, float scale, int window, const float* slopes, int dtype,
-                        void* stream);
+                        int n_kv_heads, int dim, int vdim, float scale, int window, const float* slopes, float* ws,
+                        long long ws_floats, int dtype, void* stream);
 
 /* The same attention on the tcgen05 tensor cores for prompt portions (16-bit dtypes, dim and vdim multiples of 64 up
  * to 256, page_size 64; pg_attention_ragged_tc_ok tells).  `tiles` (device int32 [n_tiles][4]) cuts the step's tokens
@@ -301,6 +302,10 @@ int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int ld_q, const
 /* xIELU: z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2;  (p, q) = pq[0..1] in
  * the model dtype.  out may alias z. */
 int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, void* stream);
+
+/* out[r, c] = silu(gate_up[r, c]) * gate_up[r, F + c] for a [rows, 2F] matrix (model dtype): the pairing of a stacked
+ * gate/up projection that was computed without it (the weight-streaming kernels of decode-sized steps). */
+int pg_swiglu(void* out, const void* gate_up, int rows, int F, int dtype, void* stream);
 
 /* ---- mixture of experts ---------------------------------------------------------------------------------------
  * pg_moe_route: z = h W_router^T in fp32, s = softmax(z) over all n_route outputs, the `top` largest of

@@ -13,7 +13,9 @@
 // same token and its neighbours, so the key / value rows they share are served by L1.
 //
 // attention_ragged_split_kernel: decode-sized batches (a handful of tokens): the keys of one (token, head) are split
-// over the warps of a CTA and the partial (max, sum, acc) triples are merged through shared memory.
+// over key slices (CTAs) and over the warps of a CTA; the partial (max, sum, acc) triples are merged through shared
+// memory and, across slices, through a caller-owned fp32 workspace by attention_ragged_merge_kernel, always in a
+// fixed order.  A lane owns ceil(vdim / 32) contiguous value columns, fetched with one vector load per key.
 #include "common.cuh"
 
 namespace pg {
@@ -33,6 +35,27 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* 
     for (int c = 0; c < dim; ++c) acc = fmaf(qs[c], to_f<T>(kp[c]), acc);
   }
   return acc;
+}
+
+// DPL contiguous elements (4, 8 or 16 bytes, aligned: the caller checks the row width) as floats
+template <typename T, int DPL>
+__device__ __forceinline__ void load_cols(const T* __restrict__ src, float* f) {
+  constexpr int BYTES = DPL * (int)sizeof(T);
+  if constexpr (BYTES == 16) {
+    const uint4 u = *reinterpret_cast<const uint4*>(src);
+    if constexpr (sizeof(T) == 4) { f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w); }
+    else unpack<T>(u, f);
+  } else if constexpr (BYTES == 8) {
+    const uint2 u = *reinterpret_cast<const uint2*>(src);
+    if constexpr (sizeof(T) == 4) { f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); }
+    else { const T* t = reinterpret_cast<const T*>(&u); for (int i = 0; i < 4; ++i) f[i] = to_f<T>(t[i]); }
+  } else if constexpr (BYTES == 4) {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(src);
+    if constexpr (sizeof(T) == 4) f[0] = __uint_as_float(u);
+    else { const T* t = reinterpret_cast<const T*>(&u); f[0] = to_f<T>(t[0]); f[1] = to_f<T>(t[1]); }
+  } else {
+    for (int i = 0; i < DPL; ++i) f[i] = to_f<T>(src[i]);
+  }
 }
 
 struct RagAttnParams {
@@ -71,14 +94,21 @@ __device__ __forceinline__ void attend_range(const RagAttnParams& p, const float
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] *= corr;
     const int n = min(32, hi - j0 + 1);
+    const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16;   // lane = DPL contiguous columns
+#pragma unroll 2
     for (int jj = 0; jj < n; ++jj) {
       const float w = __shfl_sync(0xffffffffu, pj, jj);
       const long long r = __shfl_sync(0xffffffffu, row, jj);
-      const T* vp = vpool + r * vw + g * p.vdim;
+      const T* vp = vpool + r * vw + g * p.vdim + lane * DPL;
+      if (vecv) {
+        float f[DPL];
+        load_cols<T, DPL>(vp, f);
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) {
-        const int c = lane + 32 * i;
-        if (c < p.vdim) acc[i] = fmaf(w, to_f<T>(vp[c]), acc[i]);
+        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(w, f[i], acc[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i)
+          if (lane * DPL + i < p.vdim) acc[i] = fmaf(w, to_f<T>(vp[i]), acc[i]);
       }
     }
     m = m_new;
@@ -93,7 +123,7 @@ __device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, 
   const float inv = 1.f / l;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
-    const int c = lane + 32 * i;
+    const int c = lane * DPL + i;
     if (c < p.vdim) {
       float v = acc[i] * inv;
       if (gt) v *= 1.f / (1.f + expf(-to_f<T>(gt[c])));
@@ -124,9 +154,10 @@ __global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) 
   store_out<T, DPL>(p, t, h, l, acc);
 }
 
-// One CTA per (token, head); warp w takes the key blocks w, w + warps, ... of the window.
+// One CTA per (token, head, key slice); warp w takes the key blocks w, w + warps, ... of its slice.  With one slice
+// the CTA writes the output row; with several it leaves (max, sum, acc) in the workspace for the merge kernel.
 template <typename T, int DPL>
-__global__ void __launch_bounds__(256) attention_ragged_split_kernel(RagAttnParams p) {
+__global__ void __launch_bounds__(256) attention_ragged_split_kernel(RagAttnParams p, float* __restrict__ ws) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x / p.H, h = blockIdx.x % p.H, g = h / (p.H / p.G);
@@ -139,42 +170,80 @@ __global__ void __launch_bounds__(256) attention_ragged_split_kernel(RagAttnPara
   const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
   const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
   const float slope = p.slopes ? p.slopes[h] : 0.f;
+  // this CTA's slice of [lo, pos]: whole 32-key blocks
+  const int blocks = (pos - lo + 32) / 32, per = (blocks + gridDim.y - 1) / gridDim.y;
+  const int b_begin = blockIdx.y * per, b_end = min(blocks, b_begin + per);
   float m = -INFINITY, l = 0.f, acc[DPL];
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
-  for (int b0 = lo + 32 * warp; b0 <= pos; b0 += 32 * warps)
-    attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, b0, min(pos, b0 + 31), m, l, acc);
+  for (int b = b_begin + warp; b < b_end; b += warps)
+    attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, lo + 32 * b, min(pos, lo + 32 * b + 31), m, l, acc);
   float* mine = part + (size_t)warp * (2 + 32 * DPL);
   if (lane == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) mine[2 + 32 * i + lane] = acc[i];
+  for (int i = 0; i < DPL; ++i) mine[2 + lane * DPL + i] = acc[i];
   __syncthreads();
   if (warp != 0) return;
   float M = -INFINITY;
   for (int w = 0; w < warps; ++w) M = fmaxf(M, part[(size_t)w * (2 + 32 * DPL)]);
-  float L = 0.f;
+  float Lsum = 0.f;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
   for (int w = 0; w < warps; ++w) {                     // fixed order: the result does not depend on timing
     const float* pw = part + (size_t)w * (2 + 32 * DPL);
     if (pw[1] == 0.f) continue;                         // this warp had no keys
     const float c = expf(pw[0] - M);
-    L += pw[1] * c;
+    Lsum += pw[1] * c;
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[i] += pw[2 + 32 * i + lane] * c;
+    for (int i = 0; i < DPL; ++i) acc[i] += pw[2 + lane * DPL + i] * c;
   }
-  store_out<T, DPL>(p, t, h, L, acc);
+  if (gridDim.y == 1) { store_out<T, DPL>(p, t, h, Lsum, acc); return; }
+  float* o = ws + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * (2 + 32 * DPL);
+  if (lane == 0) { o[0] = M; o[1] = Lsum; }
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) o[2 + lane * DPL + i] = acc[i];
+}
+
+// One warp per (token, head): merges the key slices in slice order.
+template <typename T, int DPL>
+__global__ void attention_ragged_merge_kernel(RagAttnParams p, const float* __restrict__ ws, int slices) {
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= p.n_tokens * p.H) return;
+  const float* base = ws + (size_t)item * slices * (2 + 32 * DPL);
+  float M = -INFINITY;
+  for (int s = 0; s < slices; ++s) M = fmaxf(M, base[(size_t)s * (2 + 32 * DPL)]);
+  float Lsum = 0.f, acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  for (int s = 0; s < slices; ++s) {
+    const float* pw = base + (size_t)s * (2 + 32 * DPL);
+    if (pw[1] == 0.f) continue;
+    const float c = expf(pw[0] - M);
+    Lsum += pw[1] * c;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] += pw[2 + lane * DPL + i] * c;
+  }
+  store_out<T, DPL>(p, item / p.H, item % p.H, Lsum, acc);
 }
 
 template <typename T, int DPL>
-static int launch_ragged(const RagAttnParams& p, cudaStream_t st) {
+static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats, cudaStream_t st) {
   const long long items = (long long)p.n_tokens * p.H;
   static const int split_max = env_int("PG_RAGGED_SPLIT_MAX_ITEMS", 592);   // below 4 (token, head) pairs per SM
   if (items <= split_max && (p.window <= 0 || p.window > 64)) {
-    const int warps = 8;
+    const int warps = 4;
+    // key slices until about two CTAs per SM are busy; the window bounds what a slice can hold (>= 128 keys each)
+    const int span = p.window > 0 ? p.window : 1 << 20;
+    int slices = 1;
+    while (slices < 16 && items * slices * 2 <= 296 && span / (slices * 2) >= 128 &&
+           items * slices * 2 * (2 + 32 * DPL) <= ws_floats) slices *= 2;
+    if (!ws) slices = 1;
     const size_t smem = sizeof(float) * (p.dim + (size_t)warps * (2 + 32 * DPL));
-    attention_ragged_split_kernel<T, DPL><<<(unsigned)items, warps * 32, smem, st>>>(p);
-    return check_launch("attention_ragged_split");
+    attention_ragged_split_kernel<T, DPL><<<dim3((unsigned)items, slices), warps * 32, smem, st>>>(p, ws);
+    int rc = check_launch("attention_ragged_split");
+    if (rc != PG_OK || slices == 1) return rc;
+    attention_ragged_merge_kernel<T, DPL><<<cdiv(items, 4), 128, 0, st>>>(p, ws, slices);
+    return check_launch("attention_ragged_merge");
   }
   const int warps = 8;
   const size_t smem = sizeof(float) * (size_t)warps * p.dim;
@@ -190,7 +259,7 @@ extern "C" int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_
                                    const void* k_pool, const void* v_pool, const int32_t* page_table, int pt_stride,
                                    int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens,
                                    int n_heads, int n_kv_heads, int dim, int vdim, float scale, int window,
-                                   const float* slopes, int dtype, void* stream) {
+                                   const float* slopes, float* ws, long long ws_floats, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
   PG_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_ragged: heads %d / kv heads %d",
              n_heads, n_kv_heads);
@@ -200,10 +269,10 @@ extern "C" int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_
   cudaStream_t st = (cudaStream_t)stream;
   const int dpl = (vdim + 31) / 32;
   PG_DISPATCH_DTYPE(dtype, T, {
-    if (dpl <= 1) return launch_ragged<T, 1>(p, st);
-    if (dpl <= 2) return launch_ragged<T, 2>(p, st);
-    if (dpl <= 4) return launch_ragged<T, 4>(p, st);
-    return launch_ragged<T, 8>(p, st);
+    if (dpl <= 1) return launch_ragged<T, 1>(p, ws, ws_floats, st);
+    if (dpl <= 2) return launch_ragged<T, 2>(p, ws, ws_floats, st);
+    if (dpl <= 4) return launch_ragged<T, 4>(p, ws, ws_floats, st);
+    return launch_ragged<T, 8>(p, ws, ws_floats, st);
   });
   return PG_OK;
 }

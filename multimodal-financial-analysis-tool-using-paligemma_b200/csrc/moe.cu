@@ -13,7 +13,26 @@
 
 namespace pg {
 
-// ------------------------------------------------------------------ router: one warp per token
+// ------------------------------------------------------------------ router: one CTA per token
+// The token's row sits in shared memory as fp32; warp w computes the logits of the routed outputs w, w + warps, ...
+// (16-byte weight loads when the rows allow), then warp 0 does the softmax, the top-k and the weights.
+template <typename T>
+__device__ __forceinline__ float dot_smem(const float* __restrict__ hs, const T* __restrict__ wr, int D, int lane) {
+  constexpr int V = Vec<T>::N;
+  float acc = 0.f;
+  if (D % V == 0 && (reinterpret_cast<uintptr_t>(wr) & 15) == 0) {
+    for (int k = lane * V; k < D; k += 32 * V) {
+      float f[V];
+      unpack<T>(ldg_cached(wr + k), f);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc = fmaf(hs[k + i], f[i], acc);
+    }
+  } else {
+    for (int k = lane; k < D; k += 32) acc = fmaf(hs[k], to_f<T>(wr[k]), acc);
+  }
+  return warp_sum(acc);
+}
+
 template <typename T>
 __global__ void moe_route_kernel(int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
                                  float* __restrict__ shared_gate, const T* __restrict__ h, int ldh,
@@ -21,25 +40,24 @@ __global__ void moe_route_kernel(int32_t* __restrict__ topk_idx, float* __restri
                                  const T* __restrict__ w_sg, int T_, int D, int n_route, int top, float scale) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const int t = blockIdx.x * warps + warp;
-  if (t >= T_) return;
-  float* s = smem + (size_t)warp * 2 * n_route;   // scores
-  float* c = s + n_route;                         // choice scores
+  const int t = blockIdx.x;
+  float* hs = smem;                               // [D]
+  float* s = smem + D;                            // scores [n_route]
+  float* c = s + n_route;                         // choice scores [n_route]
   const T* hr = h + (size_t)t * ldh;
-  for (int e = 0; e < n_route; ++e) {
-    const T* wr = w_router + (size_t)e * D;
-    float acc = 0.f;
-    for (int k = lane; k < D; k += 32) acc = fmaf(to_f<T>(hr[k]), to_f<T>(wr[k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) s[e] = acc;
+  for (int k = threadIdx.x; k < D; k += blockDim.x) hs[k] = to_f<T>(hr[k]);
+  __syncthreads();
+  for (int e = warp; e < n_route + 1; e += warps) {
+    if (e < n_route) {
+      const float z = dot_smem<T>(hs, w_router + (size_t)e * D, D, lane);
+      if (lane == 0) s[e] = z;
+    } else if (w_sg && shared_gate) {
+      const float z = dot_smem<T>(hs, w_sg, D, lane);
+      if (lane == 0) shared_gate[t] = 1.f / (1.f + expf(-z));
+    }
   }
-  if (w_sg && shared_gate) {
-    float acc = 0.f;
-    for (int k = lane; k < D; k += 32) acc = fmaf(to_f<T>(hr[k]), to_f<T>(w_sg[k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) shared_gate[t] = 1.f / (1.f + expf(-acc));
-  }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float mx = -INFINITY;
   for (int e = lane; e < n_route; e += 32) mx = fmaxf(mx, s[e]);
   mx = warp_max(mx);
@@ -247,10 +265,13 @@ extern "C" int pg_moe_route(int32_t* topk_idx, float* topk_w, float* shared_gate
                             int D, int n_route, int top, float scale, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
   PG_REQUIRE(top >= 1 && top <= n_route && n_route <= 4096, "moe_route: top %d of %d routed outputs", top, n_route);
-  const int warps = 4;
-  const size_t smem = sizeof(float) * warps * 2 * (size_t)n_route;
+  const int warps = n_route + 1 < 8 ? 4 : 8;
+  const size_t smem = sizeof(float) * ((size_t)D + 2 * (size_t)n_route);
+  PG_REQUIRE(smem <= 200 * 1024, "moe_route: D=%d with %d routed outputs does not fit shared memory", D, n_route);
   PG_DISPATCH_DTYPE(dtype, T, {
-    moe_route_kernel<T><<<cdiv(n_tokens, warps), warps * 32, smem, (cudaStream_t)stream>>>(
+    auto kern = moe_route_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<n_tokens, warps * 32, smem, (cudaStream_t)stream>>>(
         topk_idx, topk_w, shared_gate, (const T*)h, ldh, (const T*)w_router, (const T*)correction,
         (const T*)w_shared_gate, n_tokens, D, n_route, top, scale);
   });

@@ -108,6 +108,17 @@ __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ z, const
   }
 }
 
+// ------------------------------------------------------------------ SwiGLU pairing of a stacked [gate | up] row
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int rows, int F) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)rows * F;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / F, c = i % F;
+    const float g = to_f<T>(gu[r * 2 * F + c]), u = to_f<T>(gu[r * 2 * F + F + c]);
+    out[i] = from_f<T>(rnd<T>(g / (1.f + expf(-g))) * u);
+  }
+}
+
 }  // namespace pg
 
 using namespace pg;
@@ -160,4 +171,14 @@ extern "C" int pg_xielu(void* out, const void* z, const void* pq, long long n, i
     xielu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)z, (const T*)pq, n);
   });
   return check_launch("xielu");
+}
+
+extern "C" int pg_swiglu(void* out, const void* gate_up, int rows, int F, int dtype, void* stream) {
+  if (rows <= 0 || F <= 0) return PG_OK;
+  const long long n = (long long)rows * F;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  PG_DISPATCH_DTYPE(dtype, T, {
+    swiglu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)gate_up, rows, F);
+  });
+  return check_launch("swiglu");
 }

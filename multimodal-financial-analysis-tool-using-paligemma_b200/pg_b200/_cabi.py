@@ -67,11 +67,12 @@ SIGNATURES = {
     "pg_group_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "pg_qknorm_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
     "pg_attention_ragged": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp,
-                            _i, _vp],
+                            _vp, _ll, _i, _vp],
     "pg_attention_ragged_tc_ok": [_i, _i, _i, _i, _i, _i, _i],
     "pg_attention_ragged_tc": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i,
                                _vp, _vp, _i, _vp],
     "pg_xielu": [_vp, _vp, _vp, _ll, _i, _vp],
+    "pg_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "pg_moe_route": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "pg_moe_sort": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "pg_moe_gemm": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],

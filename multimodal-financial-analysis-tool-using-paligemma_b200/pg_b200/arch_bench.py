@@ -140,8 +140,10 @@ def _med(xs: List[float]) -> float:
 
 
 # ------------------------------------------------------------------ algorithmic work per op (one prefill of T tokens)
-def mubasun_work(s: dict, cfg: dict, T: int) -> Dict[str, tuple]:
-    """name -> (FLOPs, bytes) summed over the layers that run the op (bf16 operands, fp32 residual stream)."""
+def mubasun_work(s: dict, cfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
+    """name -> (FLOPs, bytes) summed over the layers that run the op (bf16 operands, fp32 residual stream) for one
+    step over `seqs` prompts of T1 tokens."""
+    T = T1 * seqs
     D, H, G, dim, vdim, W = s["width"], s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"]
     w: Dict[str, List[float]] = {}
 
@@ -150,7 +152,7 @@ def mubasun_work(s: dict, cfg: dict, T: int) -> Dict[str, tuple]:
         a[0] += flops
         a[1] += nbytes
 
-    keys = sum(min(t + 1, W) for t in range(T))      # (query, key) pairs per head
+    keys = seqs * sum(min(t + 1, W) for t in range(T1))      # (query, key) pairs per head
     for L in cfg["layers"]:
         own = "kv_from" not in L["mixer"]
         nq, nk, nv, ng = H * dim, G * dim if own else 0, G * vdim if own else 0, H * vdim
@@ -178,12 +180,13 @@ def mubasun_work(s: dict, cfg: dict, T: int) -> Dict[str, tuple]:
             add("shared_gate_up", 2 * T * D * 2 * S, 2 * (T * D + 2 * S * D + T * S))
             add("shared_down", 2 * T * S * D, 2 * (T * S + S * D + T * D))
             add("moe_combine", 0, 2 * Pe * D + T * D * (2 + 2 + 8))
-    add("head", 2 * D * s["vocab"], 2 * D * s["vocab"])
+    add("head", 2 * seqs * D * s["vocab"], 2 * D * s["vocab"])
     return {k: (v[0], v[1]) for k, v in w.items()}
 
 
-def gemma_work(s: dict, gcfg: dict, T: int) -> Dict[str, tuple]:
+def gemma_work(s: dict, gcfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
     t = gcfg["text_config"]
+    T = T1 * seqs
     D, F, nq, nkv, hd, Ln = t["hidden_size"], t["intermediate_size"], t["num_attention_heads"], t["num_key_value_heads"], \
         t["head_dim"], t["num_hidden_layers"]
     nqkv = (nq + 2 * nkv) * hd
@@ -191,7 +194,7 @@ def gemma_work(s: dict, gcfg: dict, T: int) -> Dict[str, tuple]:
         "t_norm": (0, Ln * 2 * T * D * 4),
         "t_qkv": (Ln * 2 * T * D * nqkv, Ln * 2 * (T * D + nqkv * D + T * nqkv)),
         "t_rope_append": (0, Ln * 2 * 2 * T * nqkv),
-        "t_attention": (Ln * 2 * T * T * nq * 2 * hd, Ln * 2 * (2 * T * nq * hd + 2 * T * nkv * hd)),   # unmasked: T x T
+        "t_attention": (Ln * 2 * T * T1 * nq * 2 * hd, Ln * 2 * (2 * T * nq * hd + 2 * T * nkv * hd)),   # unmasked: T1 keys
         "t_o": (Ln * 2 * T * nq * hd * D, Ln * 2 * (T * nq * hd + nq * hd * D + 2 * T * D)),
         "t_gate_up": (Ln * 2 * T * D * 2 * F, Ln * 2 * (T * D + 2 * F * D + T * F)),
         "t_down": (Ln * 2 * T * F * D, Ln * 2 * (T * F + F * D + 2 * T * D)),
@@ -216,7 +219,8 @@ LIKE = [("norm", "t_norm"), ("proj", "t_qkv"), ("qknorm_append", "t_rope_append"
 
 
 @torch.no_grad()
-def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, context=1024, decode_batches=(1, 8)) -> dict:
+def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, prefill_seqs=4, context=1024,
+        decode_batches=(1, 8)) -> dict:
     from .engine import PaliGemmaEngine
     from .mubasun import MubasunEngine
     dev, dtype = torch.device("cuda:0"), torch.bfloat16
@@ -228,24 +232,27 @@ def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, contex
         row = {"size": s}
         # ------------------------------------------------ Mubasun
         cfg = mubasun_config(s)
-        slots = max(decode_batches)
+        slots = max(max(decode_batches), prefill_seqs)
         eng = MubasunEngine(cfg, random_mubasun_weights(cfg, dev, dtype), device=dev, dtype=dtype,
                             kv_pool_tokens=(slots + 1) * (max(prefill_tokens, context) + 256))
         g = torch.Generator().manual_seed(1)
-        prompt = torch.randint(0, s["vocab"], (prefill_tokens,), generator=g).tolist()
+        prompts = [torch.randint(0, s["vocab"], (prefill_tokens,), generator=g).tolist() for _ in range(prefill_seqs)]
         b = eng.new_batcher(slots=slots + 1, max_seq_tokens=max(prefill_tokens, context) + 256)
+        T_all = prefill_tokens * prefill_seqs
 
-        def prefill():
-            b.admit("p")
-            b.run_entries([("p", prompt, [prefill_tokens - 1])])
+        def prefill():                                   # all prompts in ONE step of the engine
+            for i in range(prefill_seqs):
+                b.admit(("p", i))
+            b.run_entries([(("p", i), prompts[i], [prefill_tokens - 1]) for i in range(prefill_seqs)])
 
         def drop():
-            if "p" in b.slot_of:
-                b.finish("p")
+            for i in range(prefill_seqs):
+                if ("p", i) in b.slot_of:
+                    b.finish(("p", i))
         ms = timer.run(prefill, steps, warmup, setup=drop)
         drop()
-        row["prefill"] = {"tokens": prefill_tokens, "ms": round(_med(ms), 3), "tok_s": round(prefill_tokens / _med(ms) * 1e3),
-                          "min_ms": round(min(ms), 3), "max_ms": round(max(ms), 3)}
+        row["prefill"] = {"tokens": T_all, "sequences": prefill_seqs, "ms": round(_med(ms), 3),
+                          "tok_s": round(T_all / _med(ms) * 1e3), "min_ms": round(min(ms), 3), "max_ms": round(max(ms), 3)}
         eng._op_timing = True                                    # one more prefill, bracketed op by op
         for _ in range(2):
             prefill(); drop(); eng.op_times()
@@ -254,7 +261,7 @@ def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, contex
             timer.scratch.zero_(); prefill(); drop()
         times = {k: v / reps for k, v in eng.op_times().items()}
         eng._op_timing = False
-        row["prefill_ops"] = _roofline(mubasun_work(s, cfg, prefill_tokens), times, peaks)
+        row["prefill_ops"] = _roofline(mubasun_work(s, cfg, prefill_tokens, prefill_seqs), times, peaks)
         row["decode"] = {}
         for B in decode_batches:
             for i in range(B):
@@ -276,12 +283,12 @@ def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, contex
         # ------------------------------------------------ Gemma decoder at equal size
         gcfg = gemma_config(s)
         geng = PaliGemmaEngine(gcfg, random_gemma_weights(gcfg, dev, dtype), device=dev, dtype=dtype,
-                               kv_pool_tokens=(max(decode_batches) + 1) * (max(prefill_tokens, context) + 512))
-        ids = torch.randint(1, s["vocab"] - 2, (1, prefill_tokens), generator=g).to(dev)
+                               kv_pool_tokens=(max(max(decode_batches), prefill_seqs) + 1) * (max(prefill_tokens, context) + 512))
+        ids = torch.randint(1, s["vocab"] - 2, (prefill_seqs, prefill_tokens), generator=g).to(dev)
         holder = {}
 
         def g_prefill():
-            holder["kv"] = geng.new_kv(1)
+            holder["kv"] = geng.new_kv(prefill_seqs)
             geng.text_forward(ids, None, holder["kv"], logits="last")
 
         def g_drop():
@@ -289,7 +296,8 @@ def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, contex
                 holder.pop("kv").release()
         ms = timer.run(g_prefill, steps, warmup, setup=g_drop)
         g_drop()
-        grow = {"prefill": {"tokens": prefill_tokens, "ms": round(_med(ms), 3), "tok_s": round(prefill_tokens / _med(ms) * 1e3)}}
+        grow = {"prefill": {"tokens": T_all, "sequences": prefill_seqs, "ms": round(_med(ms), 3),
+                            "tok_s": round(T_all / _med(ms) * 1e3)}}
         geng._op_timing = True
         for _ in range(2):
             g_prefill(); g_drop(); geng.op_times()
@@ -297,7 +305,7 @@ def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, contex
             timer.scratch.zero_(); g_prefill(); g_drop()
         gt = {k: v / reps for k, v in geng.op_times().items()}
         geng._op_timing = False
-        grow["prefill_ops"] = _roofline(gemma_work(s, gcfg, prefill_tokens), gt, peaks)
+        grow["prefill_ops"] = _roofline(gemma_work(s, gcfg, prefill_tokens, prefill_seqs), gt, peaks)
         grow["decode"] = {}
         for B in decode_batches:
             kv = geng.new_kv(B)

@@ -142,7 +142,7 @@ class MubasunEngine(PagePool):
         self.gemm_impl = int(os.environ.get("PG_RAGGED_GEMM_IMPL", gemm_impl))
         self.moe_impl = int(os.environ.get("PG_MOE_IMPL", moe_impl))
         self.small_m_gemv = os.environ.get("PG_RAGGED_GEMV", "1") != "0"
-        self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "16"))
+        self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "1"))
         # steps of up to this many tokens (decode steps, short portions) replay a CUDA graph captured per token count
         self.graph_max_tokens = int(os.environ.get("PG_RAGGED_GRAPH_TOKENS", "16"))
         # steps of at least this many tokens run the tcgen05 attention kernel (layers whose head sizes it takes)
@@ -169,6 +169,7 @@ class MubasunEngine(PagePool):
                                               device=self.device)
         self.err_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._err_np = self.err_flag.numpy()
+        self.attn_ws = torch.empty(5 << 19, dtype=torch.float32, device=self.device)   # key-slice partials of decode steps
         if dtype != torch.float32:   # scratch of the split-K prompt GEMMs (shared with the other engines)
             from .engine import _WORKSPACES
             key = (self.device.index,)
@@ -245,11 +246,20 @@ class MubasunEngine(PagePool):
         N = w.shape[0] // 2 if epi in (cabi.EPI_GEGLU, cabi.EPI_SWIGLU) else w.shape[0]
         out = self._new(M, N, dtype=torch.float32 if out_f32 else None)
         L, st = cabi.lib(), cabi.stream()
-        if (self.small_m_gemv and M <= cabi.MAX_DECODE_BATCH and epi == cabi.EPI_NONE and not out_f32
-                and K % self.vec == 0 and a.is_contiguous()):
-            # a handful of rows (decode steps): the weight-streaming GEMV kernel of the decode path
-            cabi.check(L.pg_gemv_res(ptr(out), ptr(a), ptr(w), None, M, N, K, None, self.dt, st), "gemv")
-            return out
+        if self.small_m_gemv and M <= cabi.MAX_DECODE_BATCH and K % self.vec == 0 and a.is_contiguous():
+            # a handful of rows (decode steps): the weight-streaming GEMV kernel of the decode path; the gated pairing
+            # and the fp32 copy of the logits (rounded to the model dtype first, as the GEMM epilogue does) follow
+            if epi == cabi.EPI_NONE:
+                tmp = self._new(M, N) if out_f32 else out
+                cabi.check(L.pg_gemv_res(ptr(tmp), ptr(a), ptr(w), None, M, N, K, None, self.dt, st), "gemv")
+                if out_f32:
+                    out.copy_(tmp)
+                return out
+            if epi == cabi.EPI_SWIGLU and not out_f32:
+                gu = self._new(M, 2 * N)
+                cabi.check(L.pg_gemv_res(ptr(gu), ptr(a), ptr(w), None, M, 2 * N, K, None, self.dt, st), "gemv")
+                cabi.check(L.pg_swiglu(ptr(out), ptr(gu), M, N, self.dt, st), "swiglu")
+                return out
         cabi.check(L.pg_gemm(ptr(out), ptr(a), ptr(w), None, None, M, N, K, a.stride(0), w.stride(0), out.stride(0), 0, 0,
                              epi, 1 if out_f32 else 0, self.gemm_impl, self.dt, st), "gemm")
         return out
@@ -365,7 +375,8 @@ class MubasunEngine(PagePool):
                     cabi.check(L.pg_attention_ragged(ptr(att), att.stride(0), ptr(q), q.stride(0), ptr(gate),
                                                      proj.stride(0), ptr(kp), ptr(vp), ptr(kv.page_table), kv.max_pages,
                                                      self.page_size, ptr(d_slot), ptr(d_pos), T, m.heads, m.kv_heads, m.dim,
-                                                     m.vdim, m.scale, m.window, ptr(w["slopes"]), self.dt, st),
+                                                     m.vdim, m.scale, m.window, ptr(w["slopes"]), ptr(self.attn_ws),
+                                                     self.attn_ws.numel(), self.dt, st),
                                "attention_ragged")
             with tm("o"):
                 pend_a = self._linear(att, w["o"])

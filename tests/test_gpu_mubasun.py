@@ -109,7 +109,8 @@ def test_xielu_both_branches():
         _close(out, O.xielu(z.to(F64), p, q), 1e-5)
 
 
-def _attention_case(H, G, dim, vdim, window, scale, positions, seq_len, page_size=8, dtype=torch.float32, k_boost=None):
+def _attention_case(H, G, dim, vdim, window, scale, positions, seq_len, page_size=8, dtype=torch.float32, k_boost=None,
+                    use_ws=True):
     """One sequence whose cache rows are scattered over shuffled pages; queries at `positions`."""
     cabi, L, st = _lib()
     g = torch.Generator().manual_seed(3)
@@ -136,11 +137,13 @@ def _attention_case(H, G, dim, vdim, window, scale, positions, seq_len, page_siz
     pos = torch.tensor(positions, dtype=torch.int32)
     slopes = torch.tensor(O.head_slopes(H), dtype=torch.float32)
     out = torch.empty(n, H * vdim, dtype=dtype, device="cuda")
+    ws = torch.empty(1 << 20, dtype=torch.float32, device="cuda") if use_ws else None
     dev = [t.cuda() for t in (q, gate, kp, vp, table, slot, pos, slopes)]
     cabi.check(L.pg_attention_ragged(out.data_ptr(), H * vdim, dev[0].data_ptr(), H * dim, dev[1].data_ptr(), H * vdim,
                                      dev[2].data_ptr(), dev[3].data_ptr(), dev[4].data_ptr(), n_pages, page_size,
                                      dev[5].data_ptr(), dev[6].data_ptr(), n, H, G, dim, vdim, scale, window,
-                                     dev[7].data_ptr(), cabi.DTYPE_CODE[dtype], st))
+                                     dev[7].data_ptr(), ws.data_ptr() if ws is not None else None,
+                                     0 if ws is None else ws.numel(), cabi.DTYPE_CODE[dtype], st))
     want = O.window_attention(q.to(F64), kc.to(F64), vc.to(F64), positions, H, G, dim, vdim, scale, window)
     return out, want * torch.sigmoid(gate.to(F64))
 
@@ -157,6 +160,11 @@ def test_attention_windows_and_head_layouts(H, G, dim, vdim, window):
 def test_attention_decode_sized_batches(n_queries):
     out, want = _attention_case(4, 2, 16, 16, 150, 0.2, [299, 150, 64][:n_queries], 300)
     _rows_close(out, want, 2e-5)
+    for dims in ((2, 1, 32, 64), (2, 2, 16, 128), (1, 1, 8, 256), (3, 1, 8, 72)):     # vector loads of the value rows
+        out, want = _attention_case(*dims, 0, 0.2, [1499, 700, 64][:n_queries], 1500, page_size=64)   # key slices + merge
+        _rows_close(out, want, 2e-5)
+        out, want = _attention_case(*dims, 0, 0.2, [1499, 700, 64][:n_queries], 1500, page_size=64, use_ws=False)
+        _rows_close(out, want, 2e-5)
     out, want = _attention_case(4, 2, 16, 16, 0, 0.2, [299, 150, 64][:n_queries], 300, dtype=torch.bfloat16)
     _rows_close(out, want, 2e-2)
 
