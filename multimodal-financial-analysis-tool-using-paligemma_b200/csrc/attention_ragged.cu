@@ -135,6 +135,8 @@ __device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, 
 template <typename T, int DPL>
 __global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const long long item = (long long)blockIdx.x * warps + warp;
   if (item >= (long long)p.n_tokens * p.H) return;
@@ -159,6 +161,8 @@ __global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) 
 template <typename T, int DPL>
 __global__ void __launch_bounds__(256) attention_ragged_split_kernel(RagAttnParams p, float* __restrict__ ws) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x / p.H, h = blockIdx.x % p.H, g = h / (p.H / p.G);
   float* qs = smem;                                    // [dim]
@@ -207,6 +211,8 @@ __global__ void __launch_bounds__(256) attention_ragged_split_kernel(RagAttnPara
 // One warp per (token, head): merges the key slices in slice order.
 template <typename T, int DPL>
 __global__ void attention_ragged_merge_kernel(RagAttnParams p, const float* __restrict__ ws, int slices) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (item >= p.n_tokens * p.H) return;
   const float* base = ws + (size_t)item * slices * (2 + 32 * DPL);
@@ -239,16 +245,16 @@ static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats,
            items * slices * 2 * (2 + 32 * DPL) <= ws_floats) slices *= 2;
     if (!ws) slices = 1;
     const size_t smem = sizeof(float) * (p.dim + (size_t)warps * (2 + 32 * DPL));
-    attention_ragged_split_kernel<T, DPL><<<dim3((unsigned)items, slices), warps * 32, smem, st>>>(p, ws);
-    int rc = check_launch("attention_ragged_split");
+    int rc = launch_pdl("attention_ragged_split", attention_ragged_split_kernel<T, DPL>, dim3((unsigned)items, slices),
+                        dim3(warps * 32), smem, st, p, ws);
     if (rc != PG_OK || slices == 1) return rc;
-    attention_ragged_merge_kernel<T, DPL><<<cdiv(items, 4), 128, 0, st>>>(p, ws, slices);
-    return check_launch("attention_ragged_merge");
+    return launch_pdl("attention_ragged_merge", attention_ragged_merge_kernel<T, DPL>, dim3(cdiv(items, 4)), dim3(128), 0,
+                      st, p, (const float*)ws, slices);
   }
   const int warps = 8;
   const size_t smem = sizeof(float) * (size_t)warps * p.dim;
-  attention_ragged_kernel<T, DPL><<<cdiv(items, warps), warps * 32, smem, st>>>(p);
-  return check_launch("attention_ragged");
+  return launch_pdl("attention_ragged", attention_ragged_kernel<T, DPL>, dim3(cdiv(items, warps)), dim3(warps * 32), smem,
+                    st, p);
 }
 
 }  // namespace pg

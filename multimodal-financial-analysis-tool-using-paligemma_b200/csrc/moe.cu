@@ -39,6 +39,8 @@ __global__ void moe_route_kernel(int32_t* __restrict__ topk_idx, float* __restri
                                  const T* __restrict__ w_router, const T* __restrict__ correction,
                                  const T* __restrict__ w_sg, int T_, int D, int n_route, int top, float scale) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int t = blockIdx.x;
   float* hs = smem;                               // [D]
@@ -97,6 +99,8 @@ __global__ void moe_sort_kernel(int32_t* __restrict__ offsets, int32_t* __restri
                                 int32_t* __restrict__ pair_pos, const int32_t* __restrict__ topk_idx, int n_pairs,
                                 int top, int n_experts) {
   extern __shared__ int sm_i[];
+  pdl_launch_dependents();
+  pdl_wait();
   int* count = sm_i;                   // [n_experts]
   int* cursor = sm_i + n_experts;      // [n_experts]
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
@@ -137,6 +141,8 @@ moe_gemm_simt_kernel(T* __restrict__ out, int ldo, const T* __restrict__ A, int 
   __shared__ __align__(16) float Bs[MG_BK][MG_BN + MG_PAD];
   __shared__ __align__(16) float Us[DUAL ? MG_BK : 1][MG_BN + MG_PAD];
   __shared__ int s_tile[3];
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0) {
     int tile = blockIdx.y, e = 0, acc = 0;
     for (; e < n_experts; ++e) {
@@ -220,6 +226,8 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const T* __restrict__ 
                                    const int32_t* __restrict__ pair_pos, const float* __restrict__ topk_w,
                                    const T* __restrict__ h, int ldh, const T* __restrict__ shared_out, int lds,
                                    const float* __restrict__ shared_gate, int D, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float acc = 0.f;
@@ -238,6 +246,8 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const T* __restrict__ 
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ a, int lda,
                                    const int32_t* __restrict__ row_map, const int32_t* __restrict__ n_rows, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   if (n_rows && r >= *n_rows) return;
   const T* src = a + (size_t)row_map[r] * lda;
@@ -270,20 +280,18 @@ extern "C" int pg_moe_route(int32_t* topk_idx, float* topk_w, float* shared_gate
   PG_REQUIRE(smem <= 200 * 1024, "moe_route: D=%d with %d routed outputs does not fit shared memory", D, n_route);
   PG_DISPATCH_DTYPE(dtype, T, {
     auto kern = moe_route_kernel<T>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<n_tokens, warps * 32, smem, (cudaStream_t)stream>>>(
-        topk_idx, topk_w, shared_gate, (const T*)h, ldh, (const T*)w_router, (const T*)correction,
-        (const T*)w_shared_gate, n_tokens, D, n_route, top, scale);
+    return launch_pdl("moe_route", kern, dim3(n_tokens), dim3(warps * 32), smem, (cudaStream_t)stream, topk_idx, topk_w,
+                      shared_gate, (const T*)h, ldh, (const T*)w_router, (const T*)correction, (const T*)w_shared_gate,
+                      n_tokens, D, n_route, top, scale);
   });
-  return check_launch("moe_route");
+  return PG_OK;
 }
 
 extern "C" int pg_moe_sort(int32_t* offsets, int32_t* sorted_row, int32_t* pair_pos, const int32_t* topk_idx,
                            int n_pairs, int top, int n_experts, void* stream) {
   PG_REQUIRE(n_experts >= 1 && n_experts <= 4096 && top >= 1, "moe_sort: %d experts, top %d", n_experts, top);
-  moe_sort_kernel<<<1, 1024, sizeof(int) * 2 * (size_t)n_experts, (cudaStream_t)stream>>>(
-      offsets, sorted_row, pair_pos, topk_idx, n_pairs, top, n_experts);
-  return check_launch("moe_sort");
+  return launch_pdl("moe_sort", moe_sort_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * (size_t)n_experts,
+                    (cudaStream_t)stream, offsets, sorted_row, pair_pos, topk_idx, n_pairs, top, n_experts);
 }
 
 extern "C" int pg_moe_gemm(void* out, int ldo, const void* A, int lda, const int32_t* row_map, const void* W,
@@ -297,13 +305,12 @@ extern "C" int pg_moe_gemm(void* out, int ldo, const void* A, int lda, const int
   dim3 grid(cdiv(N, MG_BN), cdiv(n_pairs, MG_BM) + n_experts);
   PG_DISPATCH_DTYPE(dtype, T, {
     if (swiglu)
-      moe_gemm_simt_kernel<T, true><<<grid, MG_THREADS, 0, st>>>((T*)out, ldo, (const T*)A, lda, row_map, (const T*)W,
-                                                                offsets, n_experts, N, K);
-    else
-      moe_gemm_simt_kernel<T, false><<<grid, MG_THREADS, 0, st>>>((T*)out, ldo, (const T*)A, lda, row_map, (const T*)W,
-                                                                 offsets, n_experts, N, K);
+      return launch_pdl("moe_gemm", moe_gemm_simt_kernel<T, true>, grid, dim3(MG_THREADS), 0, st, (T*)out, ldo, (const T*)A,
+                        lda, row_map, (const T*)W, offsets, n_experts, N, K);
+    return launch_pdl("moe_gemm", moe_gemm_simt_kernel<T, false>, grid, dim3(MG_THREADS), 0, st, (T*)out, ldo, (const T*)A,
+                      lda, row_map, (const T*)W, offsets, n_experts, N, K);
   });
-  return check_launch("moe_gemm");
+  return PG_OK;
 }
 
 extern "C" int pg_moe_combine(float* x, const void* y, int ldy, const int32_t* pair_pos, const float* topk_w,
@@ -311,17 +318,18 @@ extern "C" int pg_moe_combine(float* x, const void* y, int ldy, const int32_t* p
                               int n_tokens, int D, int top, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
   PG_DISPATCH_DTYPE(dtype, T, {
-    moe_combine_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(x, (const T*)y, ldy, pair_pos, topk_w, (const T*)h,
-                                                                     ldh, (const T*)shared_out, lds, shared_gate, D, top);
+    return launch_pdl("moe_combine", moe_combine_kernel<T>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, x,
+                      (const T*)y, ldy, pair_pos, topk_w, (const T*)h, ldh, (const T*)shared_out, lds, shared_gate, D, top);
   });
-  return check_launch("moe_combine");
+  return PG_OK;
 }
 
 extern "C" int pg_gather_rows(void* out, const void* a, int lda, const int32_t* row_map, const int32_t* n_rows,
                               int max_rows, int cols, int dtype, void* stream) {
   if (max_rows <= 0) return PG_OK;
   PG_DISPATCH_DTYPE(dtype, T, {
-    gather_rows_kernel<T><<<max_rows, 128, 0, (cudaStream_t)stream>>>((T*)out, (const T*)a, lda, row_map, n_rows, cols);
+    return launch_pdl("gather_rows", gather_rows_kernel<T>, dim3(max_rows), dim3(128), 0, (cudaStream_t)stream, (T*)out,
+                      (const T*)a, lda, row_map, n_rows, cols);
   });
-  return check_launch("gather_rows");
+  return PG_OK;
 }

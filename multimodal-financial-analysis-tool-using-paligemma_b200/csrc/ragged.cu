@@ -13,6 +13,8 @@ template <typename T>
 __global__ void embed_pos_kernel(float* __restrict__ x, const int64_t* __restrict__ ids, const int32_t* __restrict__ pos,
                                  const T* __restrict__ emb, const T* __restrict__ pos_emb, int D, int64_t vocab,
                                  int max_pos, float emb_scale, int* err_flag) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int64_t id = ids[t];
   const int p = pos ? pos[t] : 0;
@@ -36,6 +38,8 @@ template <typename T>
 __global__ void group_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ x, const T* __restrict__ a, int lda,
                                      const T* __restrict__ b, int ldb, const T* __restrict__ w,
                                      const int32_t* __restrict__ rows_idx, int rows, int D, int groups, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (item >= rows * groups) return;
@@ -74,6 +78,8 @@ __global__ void qknorm_append_kernel(T* __restrict__ q_out, const T* __restrict_
                                      int page_size, const int32_t* __restrict__ tok_slot,
                                      const int32_t* __restrict__ tok_pos) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const T* row = proj + (size_t)t * ld;
   float ss = 0.f;
@@ -100,6 +106,8 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 
 template <typename T>
 __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __restrict__ pq, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const float ap = softplus_f(to_f<T>(pq[0])), an = 0.5f + softplus_f(to_f<T>(pq[1]));
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float v = to_f<T>(z[i]);
@@ -111,6 +119,8 @@ __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ z, const
 // ------------------------------------------------------------------ SwiGLU pairing of a stacked [gate | up] row
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int rows, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)rows * F;
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F, c = i % F;
@@ -128,10 +138,10 @@ extern "C" int pg_embed_pos(float* x, const int64_t* ids, const int32_t* positio
                             int* err_flag, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
   PG_DISPATCH_DTYPE(dtype, T, {
-    embed_pos_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(x, ids, positions, (const T*)emb, (const T*)pos_emb,
-                                                                   D, vocab, max_pos, emb_scale, err_flag);
+    return launch_pdl("embed_pos", embed_pos_kernel<T>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, x, ids, positions,
+                      (const T*)emb, (const T*)pos_emb, D, vocab, max_pos, emb_scale, err_flag);
   });
-  return check_launch("embed_pos");
+  return PG_OK;
 }
 
 extern "C" int pg_group_rmsnorm(void* out, float* x, const void* add_a, int lda, const void* add_b, int ldb,
@@ -143,10 +153,11 @@ extern "C" int pg_group_rmsnorm(void* out, float* x, const void* add_a, int lda,
   PG_REQUIRE(!rows_idx || (!add_a && !add_b), "group_rmsnorm: the residual sum takes all rows (no row index)");
   const int warps = 8;
   PG_DISPATCH_DTYPE(dtype, T, {
-    group_rmsnorm_kernel<T><<<cdiv((long long)rows * groups, warps), warps * 32, 0, (cudaStream_t)stream>>>(
-        (T*)out, x, (const T*)add_a, lda, (const T*)add_b, ldb, (const T*)w, rows_idx, rows, D, groups, eps);
+    return launch_pdl("group_rmsnorm", group_rmsnorm_kernel<T>, dim3(cdiv((long long)rows * groups, warps)), dim3(warps * 32),
+                      0, (cudaStream_t)stream, (T*)out, x, (const T*)add_a, lda, (const T*)add_b, ldb, (const T*)w, rows_idx,
+                      rows, D, groups, eps);
   });
-  return check_launch("group_rmsnorm");
+  return PG_OK;
 }
 
 extern "C" int pg_qknorm_append(void* q_out, const void* proj, int ld, int q_col0, int q_cols, int k_col0, int k_cols,
@@ -157,20 +168,21 @@ extern "C" int pg_qknorm_append(void* q_out, const void* proj, int ld, int q_col
   PG_REQUIRE(k_cols == 0 || (k_pool && v_pool && page_table && tok_slot && tok_pos && page_size > 0),
              "qknorm_append: a layer with keys of its own needs the pools and the token map");
   PG_DISPATCH_DTYPE(dtype, T, {
-    qknorm_append_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
-        (T*)q_out, (const T*)proj, ld, q_col0, q_cols, k_col0, k_cols, v_col0, v_cols, (const T*)q_w, (const T*)k_w, eps,
-        (T*)k_pool, (T*)v_pool, page_table, pt_stride, page_size, tok_slot, tok_pos);
+    return launch_pdl("qknorm_append", qknorm_append_kernel<T>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream,
+                      (T*)q_out, (const T*)proj, ld, q_col0, q_cols, k_col0, k_cols, v_col0, v_cols, (const T*)q_w,
+                      (const T*)k_w, eps, (T*)k_pool, (T*)v_pool, page_table, pt_stride, page_size, tok_slot, tok_pos);
   });
-  return check_launch("qknorm_append");
+  return PG_OK;
 }
 
 extern "C" int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, void* stream) {
   if (n <= 0) return PG_OK;
   const int blocks = (int)((n + 1023) / 1024 < 148 * 8 ? (n + 1023) / 1024 : 148 * 8);
   PG_DISPATCH_DTYPE(dtype, T, {
-    xielu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)z, (const T*)pq, n);
+    return launch_pdl("xielu", xielu_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)z,
+                      (const T*)pq, n);
   });
-  return check_launch("xielu");
+  return PG_OK;
 }
 
 extern "C" int pg_swiglu(void* out, const void* gate_up, int rows, int F, int dtype, void* stream) {
@@ -178,7 +190,8 @@ extern "C" int pg_swiglu(void* out, const void* gate_up, int rows, int F, int dt
   const long long n = (long long)rows * F;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   PG_DISPATCH_DTYPE(dtype, T, {
-    swiglu_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)gate_up, rows, F);
+    return launch_pdl("swiglu", swiglu_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                      (const T*)gate_up, rows, F);
   });
-  return check_launch("swiglu");
+  return PG_OK;
 }
