@@ -25,12 +25,28 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* 
   constexpr int V = Vec<T>::N;
   float acc = 0.f;
   if ((dim % V) == 0 && (reinterpret_cast<uintptr_t>(kp) & 15) == 0) {
-    for (int c = 0; c < dim; c += V) {
+    int c = 0;
+    float a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (; c + 4 * V <= dim; c += 4 * V) {          // four loads in flight, four independent accumulators
+      const uint4 u0 = *reinterpret_cast<const uint4*>(kp + c), u1 = *reinterpret_cast<const uint4*>(kp + c + V),
+                  u2 = *reinterpret_cast<const uint4*>(kp + c + 2 * V), u3 = *reinterpret_cast<const uint4*>(kp + c + 3 * V);
+      float f0[V], f1[V], f2[V], f3[V];
+      unpack<T>(u0, f0); unpack<T>(u1, f1); unpack<T>(u2, f2); unpack<T>(u3, f3);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        acc = fmaf(qs[c + i], f0[i], acc);
+        a1 = fmaf(qs[c + V + i], f1[i], a1);
+        a2 = fmaf(qs[c + 2 * V + i], f2[i], a2);
+        a3 = fmaf(qs[c + 3 * V + i], f3[i], a3);
+      }
+    }
+    for (; c < dim; c += V) {
       float f[V];
       unpack<T>(*reinterpret_cast<const uint4*>(kp + c), f);
 #pragma unroll
       for (int i = 0; i < V; ++i) acc = fmaf(qs[c + i], f[i], acc);
     }
+    acc += a1 + a2 + a3;
   } else {
     for (int c = 0; c < dim; ++c) acc = fmaf(qs[c], to_f<T>(kp[c]), acc);
   }
@@ -95,7 +111,7 @@ __device__ __forceinline__ void attend_range(const RagAttnParams& p, const float
     for (int i = 0; i < DPL; ++i) acc[i] *= corr;
     const int n = min(32, hi - j0 + 1);
     const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16;   // lane = DPL contiguous columns
-#pragma unroll 2
+#pragma unroll 8
     for (int jj = 0; jj < n; ++jj) {
       const float w = __shfl_sync(0xffffffffu, pj, jj);
       const long long r = __shfl_sync(0xffffffffu, row, jj);

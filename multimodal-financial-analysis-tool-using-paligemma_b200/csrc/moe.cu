@@ -318,7 +318,8 @@ extern "C" int pg_moe_combine(float* x, const void* y, int ldy, const int32_t* p
                               int n_tokens, int D, int top, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
   PG_DISPATCH_DTYPE(dtype, T, {
-    return launch_pdl("moe_combine", moe_combine_kernel<T>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, x,
+    const int threads = n_tokens <= 64 ? (D >= 2048 ? 512 : 256) : 128;
+    return launch_pdl("moe_combine", moe_combine_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, x,
                       (const T*)y, ldy, pair_pos, topk_w, (const T*)h, ldh, (const T*)shared_out, lds, shared_gate, D, top);
   });
   return PG_OK;

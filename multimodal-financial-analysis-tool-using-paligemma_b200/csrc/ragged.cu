@@ -168,7 +168,9 @@ extern "C" int pg_qknorm_append(void* q_out, const void* proj, int ld, int q_col
   PG_REQUIRE(k_cols == 0 || (k_pool && v_pool && page_table && tok_slot && tok_pos && page_size > 0),
              "qknorm_append: a layer with keys of its own needs the pools and the token map");
   PG_DISPATCH_DTYPE(dtype, T, {
-    return launch_pdl("qknorm_append", qknorm_append_kernel<T>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream,
+    // a handful of tokens (decode steps): wide CTAs, so that a row is a few loads per thread
+    const int threads = n_tokens <= 64 ? (q_cols >= 2048 ? 512 : 256) : 128;
+    return launch_pdl("qknorm_append", qknorm_append_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream,
                       (T*)q_out, (const T*)proj, ld, q_col0, q_cols, k_col0, k_cols, v_col0, v_cols, (const T*)q_w,
                       (const T*)k_w, eps, (T*)k_pool, (T*)v_pool, page_table, pt_stride, page_size, tok_slot, tok_pos);
   });

@@ -84,6 +84,21 @@ _RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_att
 _lib = None
 
 
+def ensure_built() -> None:
+    """Build the CUDA library with the Makefile beside the sources if this checkout has none yet (the command-line
+    programs call this first; everything else raises when the library is missing)."""
+    import subprocess
+    import sys
+    if os.path.exists(LIB_PATH):
+        return
+    jobs = os.environ.get("MAX_JOBS") or str(os.cpu_count() or 4)
+    r = subprocess.run(["make", "-C", os.path.join(os.path.dirname(_HERE), "csrc"), "-j", jobs], stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0 or not os.path.exists(LIB_PATH):
+        sys.stderr.write(r.stdout[-4000:])
+        raise RuntimeError("building the CUDA library failed")
+
+
 def lib() -> C.CDLL:
     """Load the CUDA library once; raise loudly if it has not been built."""
     global _lib

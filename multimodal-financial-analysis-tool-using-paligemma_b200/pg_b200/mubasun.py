@@ -142,6 +142,9 @@ class MubasunEngine(PagePool):
         self.gemm_impl = int(os.environ.get("PG_RAGGED_GEMM_IMPL", gemm_impl))
         self.moe_impl = int(os.environ.get("PG_MOE_IMPL", moe_impl))
         self.small_m_gemv = os.environ.get("PG_RAGGED_GEMV", "1") != "0"
+        # rows up to which a projection streams its weights through the GEMV kernel; from there on the 16-bit path
+        # takes the tensor-core GEMMs (the GEMV turns ALU-bound as rows are added), fp32 keeps it to its 8-row limit
+        self.gemv_max_rows = cabi.MAX_DECODE_BATCH if dtype == torch.float32 else max(1, cabi.BATCHED_DECODE_MIN - 1)
         self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "1"))
         # steps of up to this many tokens (decode steps, short portions) replay a CUDA graph captured per token count
         self.graph_max_tokens = int(os.environ.get("PG_RAGGED_GRAPH_TOKENS", "16"))
@@ -246,7 +249,7 @@ class MubasunEngine(PagePool):
         N = w.shape[0] // 2 if epi in (cabi.EPI_GEGLU, cabi.EPI_SWIGLU) else w.shape[0]
         out = self._new(M, N, dtype=torch.float32 if out_f32 else None)
         L, st = cabi.lib(), cabi.stream()
-        if self.small_m_gemv and M <= cabi.MAX_DECODE_BATCH and K % self.vec == 0 and a.is_contiguous():
+        if self.small_m_gemv and M <= self.gemv_max_rows and K % self.vec == 0 and a.is_contiguous():
             # a handful of rows (decode steps): the weight-streaming GEMV kernel of the decode path; the gated pairing
             # and the fp32 copy of the logits (rounded to the model dtype first, as the GEMM epilogue does) follow
             if epi == cabi.EPI_NONE:
