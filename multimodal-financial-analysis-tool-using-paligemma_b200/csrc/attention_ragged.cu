@@ -12,10 +12,11 @@
 // value columns and walk the 32 keys with the weights broadcast by shuffles.  Warps of a CTA are the heads of the
 // same token and its neighbours, so the key / value rows they share are served by L1.
 //
-// attention_ragged_split_kernel: decode-sized batches (a handful of tokens): the keys of one (token, head) are split
-// over key slices (CTAs) and over the warps of a CTA; the partial (max, sum, acc) triples are merged through shared
-// memory and, across slices, through a caller-owned fp32 workspace by attention_ragged_merge_kernel, always in a
-// fixed order.  A lane owns ceil(vdim / 32) contiguous value columns, fetched with one vector load per key.
+// attention_ragged_split_kernel: decode-sized batches (a handful of tokens): one CTA per (token, key/value head, key
+// slice) serves all query heads of the group from ONE read of every key and value row; the keys are split over key
+// slices (CTAs) and over the warps of a CTA; the partial (max, sum, acc) triples are merged through shared memory
+// and, across slices, through a caller-owned fp32 workspace by attention_ragged_merge_kernel, always in a fixed
+// order.  A lane owns ceil(vdim / 32) contiguous value columns, fetched with one vector load per key.
 #include "common.cuh"
 
 namespace pg {
@@ -172,56 +173,140 @@ __global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) 
   store_out<T, DPL>(p, t, h, l, acc);
 }
 
-// One CTA per (token, head, key slice); warp w takes the key blocks w, w + warps, ... of its slice.  With one slice
-// the CTA writes the output row; with several it leaves (max, sum, acc) in the workspace for the merge kernel.
-template <typename T, int DPL>
-__global__ void __launch_bounds__(256) attention_ragged_split_kernel(RagAttnParams p, float* __restrict__ ws) {
+// R query rows against one key row: one pass over the key, R independent accumulators.
+template <typename T, int R>
+__device__ __forceinline__ void dot_rows(const float* __restrict__ qs, int dim, const T* __restrict__ kp, float* out) {
+  constexpr int V = Vec<T>::N;
+#pragma unroll
+  for (int r = 0; r < R; ++r) out[r] = 0.f;
+  if ((dim % V) == 0 && (reinterpret_cast<uintptr_t>(kp) & 15) == 0) {
+#pragma unroll 2
+    for (int c = 0; c < dim; c += V) {
+      float f[V];
+      unpack<T>(*reinterpret_cast<const uint4*>(kp + c), f);
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[r] = fmaf(qs[r * dim + c + i], f[i], out[r]);
+    }
+  } else {
+    for (int c = 0; c < dim; ++c) {
+      const float kv = to_f<T>(kp[c]);
+#pragma unroll
+      for (int r = 0; r < R; ++r) out[r] = fmaf(qs[r * dim + c], kv, out[r]);
+    }
+  }
+}
+
+// One CTA per (token, key/value head, key slice): the R = H / G query heads that share the key/value head are
+// handled together, so every key and value row is read once for all of them.  Warp w takes the key blocks w,
+// w + warps, ... of its slice.  With one slice the CTA writes the output rows; with several it leaves (max, sum, acc)
+// per query head in the workspace for the merge kernel.
+template <typename T, int DPL, int R>
+__global__ void __launch_bounds__(128) attention_ragged_split_kernel(RagAttnParams p, float* __restrict__ ws) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
+  constexpr int PW = 2 + 32 * DPL;                     // floats of one partial
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const int t = blockIdx.x / p.H, h = blockIdx.x % p.H, g = h / (p.H / p.G);
-  float* qs = smem;                                    // [dim]
-  float* part = smem + p.dim;                          // [warps][2 + 32 * DPL]
-  const T* qr = reinterpret_cast<const T*>(p.q) + (size_t)t * p.ld_q + h * p.dim;
-  for (int c = threadIdx.x; c < p.dim; c += blockDim.x) qs[c] = to_f<T>(qr[c]);
+  const int t = blockIdx.x / p.G, g = blockIdx.x % p.G, h0 = g * R;
+  float* qs = smem;                                    // [R][dim]
+  float* part = smem + R * p.dim;                      // [warps][R][PW]
+  const T* qr = reinterpret_cast<const T*>(p.q) + (size_t)t * p.ld_q + h0 * p.dim;
+  for (int c = threadIdx.x; c < R * p.dim; c += blockDim.x) qs[c] = to_f<T>(qr[c]);
   __syncthreads();
   const int pos = p.tok_pos[t];
   const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
   const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-  const float slope = p.slopes ? p.slopes[h] : 0.f;
+  float slope[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) slope[r] = p.slopes ? p.slopes[h0 + r] : 0.f;
+  const T* kpool = reinterpret_cast<const T*>(p.k_pool);
+  const T* vpool = reinterpret_cast<const T*>(p.v_pool);
+  const int kw = p.G * p.dim, vw = p.G * p.vdim;
+  const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16;
   // this CTA's slice of [lo, pos]: whole 32-key blocks
   const int blocks = (pos - lo + 32) / 32, per = (blocks + gridDim.y - 1) / gridDim.y;
   const int b_begin = blockIdx.y * per, b_end = min(blocks, b_begin + per);
-  float m = -INFINITY, l = 0.f, acc[DPL];
+  float m[R], l[R], acc[R][DPL];
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
-  for (int b = b_begin + warp; b < b_end; b += warps)
-    attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, lo + 32 * b, min(pos, lo + 32 * b + 31), m, l, acc);
-  float* mine = part + (size_t)warp * (2 + 32 * DPL);
-  if (lane == 0) { mine[0] = m; mine[1] = l; }
+  for (int r = 0; r < R; ++r) {
+    m[r] = -INFINITY; l[r] = 0.f;
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) mine[2 + lane * DPL + i] = acc[i];
-  __syncthreads();
-  if (warp != 0) return;
-  float M = -INFINITY;
-  for (int w = 0; w < warps; ++w) M = fmaxf(M, part[(size_t)w * (2 + 32 * DPL)]);
-  float Lsum = 0.f;
-#pragma unroll
-  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
-  for (int w = 0; w < warps; ++w) {                     // fixed order: the result does not depend on timing
-    const float* pw = part + (size_t)w * (2 + 32 * DPL);
-    if (pw[1] == 0.f) continue;                         // this warp had no keys
-    const float c = expf(pw[0] - M);
-    Lsum += pw[1] * c;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[i] += pw[2 + lane * DPL + i] * c;
+    for (int i = 0; i < DPL; ++i) acc[r][i] = 0.f;
   }
-  if (gridDim.y == 1) { store_out<T, DPL>(p, t, h, Lsum, acc); return; }
-  float* o = ws + ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * (2 + 32 * DPL);
-  if (lane == 0) { o[0] = M; o[1] = Lsum; }
+  for (int b = b_begin + warp; b < b_end; b += warps) {
+    const int j0 = lo + 32 * b, hi = min(pos, j0 + 31), j = j0 + lane;
+    const bool valid = j <= hi;
+    long long row = 0;
+    float s[R], pj[R];
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) o[2 + lane * DPL + i] = acc[i];
+    for (int r = 0; r < R; ++r) s[r] = -INFINITY;
+    if (valid) {
+      row = (long long)pt_row[j / p.page_size] * p.page_size + j % p.page_size;
+      dot_rows<T, R>(qs, p.dim, kpool + row * kw + g * p.dim, s);
+#pragma unroll
+      for (int r = 0; r < R; ++r) s[r] = s[r] * p.scale - slope[r] * (float)(pos - j);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float m_new = fmaxf(m[r], warp_max(s[r]));
+      const float corr = expf(m[r] - m_new);
+      pj[r] = valid ? expf(s[r] - m_new) : 0.f;
+      l[r] = l[r] * corr + warp_sum(pj[r]);
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[r][i] *= corr;
+      m[r] = m_new;
+    }
+    const int n = hi - j0 + 1;
+#pragma unroll 4
+    for (int jj = 0; jj < n; ++jj) {
+      const long long vr = __shfl_sync(0xffffffffu, row, jj);
+      const T* vp = vpool + vr * vw + g * p.vdim + lane * DPL;
+      float f[DPL];
+      if (vecv) {
+        load_cols<T, DPL>(vp, f);
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) f[i] = (lane * DPL + i < p.vdim) ? to_f<T>(vp[i]) : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float w = __shfl_sync(0xffffffffu, pj[r], jj);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[r][i] = fmaf(w, f[i], acc[r][i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float* mine = part + ((size_t)warp * R + r) * PW;
+    if (lane == 0) { mine[0] = m[r]; mine[1] = l[r]; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) mine[2 + lane * DPL + i] = acc[r][i];
+  }
+  __syncthreads();
+  // warp r (and r + warps, ...) merges query head r over the warps, in warp order
+  for (int r = warp; r < R; r += warps) {
+    float M = -INFINITY;
+    for (int w = 0; w < warps; ++w) M = fmaxf(M, part[((size_t)w * R + r) * PW]);
+    float Lsum = 0.f, a[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) a[i] = 0.f;
+    for (int w = 0; w < warps; ++w) {
+      const float* pw = part + ((size_t)w * R + r) * PW;
+      if (pw[1] == 0.f) continue;                       // this warp had no keys
+      const float c = expf(pw[0] - M);
+      Lsum += pw[1] * c;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) a[i] += pw[2 + lane * DPL + i] * c;
+    }
+    if (gridDim.y == 1) { store_out<T, DPL>(p, t, h0 + r, Lsum, a); continue; }
+    float* o = ws + (((size_t)t * p.H + h0 + r) * gridDim.y + blockIdx.y) * PW;
+    if (lane == 0) { o[0] = M; o[1] = Lsum; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[2 + lane * DPL + i] = a[i];
+  }
 }
 
 // One warp per (token, head): merges the key slices in slice order.
@@ -248,24 +333,38 @@ __global__ void attention_ragged_merge_kernel(RagAttnParams p, const float* __re
   store_out<T, DPL>(p, item / p.H, item % p.H, Lsum, acc);
 }
 
+template <typename T, int DPL, int R>
+static int launch_split(const RagAttnParams& p, float* ws, int slices, cudaStream_t st) {
+  const int warps = 4;
+  const size_t smem = sizeof(float) * ((size_t)R * p.dim + (size_t)warps * R * (2 + 32 * DPL));
+  const long long items = (long long)p.n_tokens * p.H;
+  int rc = launch_pdl("attention_ragged_split", attention_ragged_split_kernel<T, DPL, R>,
+                      dim3((unsigned)(p.n_tokens * p.G), slices), dim3(warps * 32), smem, st, p, ws);
+  if (rc != PG_OK || slices == 1) return rc;
+  return launch_pdl("attention_ragged_merge", attention_ragged_merge_kernel<T, DPL>, dim3(cdiv(items, 4)), dim3(128), 0,
+                    st, p, (const float*)ws, slices);
+}
+
 template <typename T, int DPL>
 static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats, cudaStream_t st) {
   const long long items = (long long)p.n_tokens * p.H;
   static const int split_max = env_int("PG_RAGGED_SPLIT_MAX_ITEMS", 592);   // below 4 (token, head) pairs per SM
-  if (items <= split_max && (p.window <= 0 || p.window > 64)) {
-    const int warps = 4;
-    // key slices until about two CTAs per SM are busy; the window bounds what a slice can hold (>= 128 keys each)
+  const int R = p.H / p.G;
+  const bool r_ok = R == 1 || R == 2 || R == 4 || (R == 8 && DPL <= 4);
+  if (items <= split_max && r_ok && (p.window <= 0 || p.window > 64)) {
+    // key slices until about two CTAs per SM are busy; a slice holds at least 128 keys (one block per warp)
+    const long long ctas = (long long)p.n_tokens * p.G;
     const int span = p.window > 0 ? p.window : 1 << 20;
     int slices = 1;
-    while (slices < 16 && items * slices * 2 <= 296 && span / (slices * 2) >= 128 &&
+    while (slices < 32 && ctas * slices * 2 <= 296 && span / (slices * 2) >= 128 &&
            items * slices * 2 * (2 + 32 * DPL) <= ws_floats) slices *= 2;
     if (!ws) slices = 1;
-    const size_t smem = sizeof(float) * (p.dim + (size_t)warps * (2 + 32 * DPL));
-    int rc = launch_pdl("attention_ragged_split", attention_ragged_split_kernel<T, DPL>, dim3((unsigned)items, slices),
-                        dim3(warps * 32), smem, st, p, ws);
-    if (rc != PG_OK || slices == 1) return rc;
-    return launch_pdl("attention_ragged_merge", attention_ragged_merge_kernel<T, DPL>, dim3(cdiv(items, 4)), dim3(128), 0,
-                      st, p, (const float*)ws, slices);
+    switch (R) {
+      case 1: return launch_split<T, DPL, 1>(p, ws, slices, st);
+      case 2: return launch_split<T, DPL, 2>(p, ws, slices, st);
+      case 4: return launch_split<T, DPL, 4>(p, ws, slices, st);
+      default: return launch_split<T, (DPL <= 4 ? DPL : 4), 8>(p, ws, slices, st);
+    }
   }
   const int warps = 8;
   const size_t smem = sizeof(float) * (size_t)warps * p.dim;
