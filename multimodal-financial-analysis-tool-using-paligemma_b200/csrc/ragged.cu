@@ -105,15 +105,24 @@ __global__ void qknorm_append_kernel(T* __restrict__ q_out, const T* __restrict_
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 template <typename T>
-__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __restrict__ pq, long long n) {
+__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __restrict__ pq, long long n, int vec) {
   pdl_launch_dependents();
   pdl_wait();
+  constexpr int V = Vec<T>::N;
   const float ap = softplus_f(to_f<T>(pq[0])), an = 0.5f + softplus_f(to_f<T>(pq[1]));
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const float v = to_f<T>(z[i]);
-    const float r = v > 0.f ? ap * v * v + 0.5f * v : an * (expm1f(v) - v) + 0.5f * v;
-    out[i] = from_f<T>(r);
+  auto act = [&](float v) { return v > 0.f ? ap * v * v + 0.5f * v : an * (expm1f(v) - v) + 0.5f * v; };
+  const long long stride = (long long)gridDim.x * blockDim.x, first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (vec) {   // 16-byte accesses (n a multiple of the vector width, aligned pointers: checked on the host)
+    for (long long i = first; i < n / V; i += stride) {
+      float f[V];
+      unpack<T>(*reinterpret_cast<const uint4*>(z + i * V), f);
+#pragma unroll
+      for (int k = 0; k < V; ++k) f[k] = act(f[k]);
+      *reinterpret_cast<uint4*>(out + i * V) = pack<T>(f);
+    }
+    return;
   }
+  for (long long i = first; i < n; i += stride) out[i] = from_f<T>(act(to_f<T>(z[i])));
 }
 
 // ------------------------------------------------------------------ SwiGLU pairing of a stacked [gate | up] row
@@ -179,10 +188,13 @@ extern "C" int pg_qknorm_append(void* q_out, const void* proj, int ld, int q_col
 
 extern "C" int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, void* stream) {
   if (n <= 0) return PG_OK;
-  const int blocks = (int)((n + 1023) / 1024 < 148 * 8 ? (n + 1023) / 1024 : 148 * 8);
   PG_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = Vec<T>::N;
+    const int vec = (n % V == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)z % 16) == 0) ? 1 : 0;
+    const long long work = vec ? n / V : n;
+    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
     return launch_pdl("xielu", xielu_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)z,
-                      (const T*)pq, n);
+                      (const T*)pq, n, vec);
   });
   return PG_OK;
 }
