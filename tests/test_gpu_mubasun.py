@@ -362,6 +362,43 @@ def test_prefill_equals_token_by_token_and_portions(name):
     b.close()
 
 
+MID = O.make_config(width=384, groups=2, vocab=600, max_positions=512, layers=[
+    O.layer(O.attn(heads=6, kv_heads=3, dim=64, vdim=64, window=150, scale=0.125), O.dense(640)),
+    O.layer(O.attn(heads=6, kv_heads=3, dim=64, vdim=64, window=40, scale=0.125, kv_from=0),
+            O.moe(experts=6, identity=1, top=2, ff=128, shared=192)),
+    O.layer(O.attn(heads=4, kv_heads=1, dim=128, vdim=64, window=0, scale=0.09), O.moe(experts=3, identity=0, top=1, ff=256, shared=0))])
+
+
+WIDE = O.make_config(width=1024, groups=8, vocab=1000, max_positions=512, layers=[
+    O.layer(O.attn(heads=8, kv_heads=2, dim=128, vdim=128, window=200, scale=0.088), O.moe(experts=4, identity=1, top=2, ff=512, shared=256)),
+    O.layer(O.attn(heads=8, kv_heads=2, dim=128, vdim=128, window=64, scale=0.088, kv_from=0), O.dense(2048))])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("which", ["mid", "wide"])
+def test_mid_size_model_portions_of_every_gemm_regime(dtype, which):
+    """Wide enough that the 16-bit run takes every projection path of the library: CTA-pair / single-CTA tiles for
+    the whole prompt, the skinny and split-K kernels for portions of 4..128 tokens, the weight-streaming kernel for
+    1..3 tokens, the tensor-core attention from 48 tokens on and the CUDA-graph step below 17."""
+    cfg = MID if which == "mid" else WIDE
+    eng, orc = _engine(cfg, seed=37, dtype=dtype, pool_tokens=1024)
+    toks = _tokens(330, cfg["vocab"], 12)
+    want = orc.logits(toks)
+    stray = 0.0 if dtype == torch.float32 else 0.2
+    b = eng.new_batcher(slots=2)
+    b.admit("whole")
+    _rows_close(b.run_entries([("whole", toks, list(range(len(toks))))]), want, TOL[dtype], stray)
+    b.admit("parts")
+    at, parts = 0, []
+    for n in (5, 17, 64, 100, 3, 48, 1, 2, 70, 4, 16):
+        parts.append(b.run_entries([("parts", toks[at:at + n], list(range(n)))]))
+        at += n
+    assert at == len(toks)
+    _rows_close(torch.cat(parts), want, TOL[dtype], stray)
+    eng.check_errors(sync=True)
+    b.close()
+
+
 def test_unequal_requests_in_one_batch_equal_each_alone_and_slots_and_pages_are_reused():
     cfg = CONFIGS["small"]
     eng, orc = _engine(cfg, seed=17, pool_tokens=4 * 64)               # four pages for everything
