@@ -7,7 +7,7 @@
 // before this launch).  Two passes over the key tiles, both on the tensor cores, as in attention_tc.cu:
 //   pass 0: S = Q K^T (tcgen05.mma, fp32 in TMEM) -> thread r owns query row r: s = S * scale - slope_h * (i - j),
 //           masked outside 0 <= i - j < window, running row maximum (no shuffles);
-//   pass 1: S again, p = exp(s - max) in fp32, row sum from the fp32 values, P rounded to the model dtype into a
+//   pass 1: S again (K double-buffered, V in one buffer), p = exp(s - max) in fp32, row sum from the fp32 values, P rounded to the model dtype into a
 //           K-major SWIZZLE_128B tile, O += P V with V as an MN-major operand straight from its [key, vdim] page.
 // Epilogue: O / sum, times sigmoid(gate), rounded once.  Key width and value width are independent multiples of 64.
 // Every mbarrier wait is bounded: a wait that gives up sets the error flag, the roles leave their loops, the CTA lets
@@ -62,12 +62,14 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t s_q = base, s_kv = s_q + Q_BYTES, s_p = s_kv + 2 * (K_BYTES + V_BYTES);
-  auto s_k = [&](int bf) { return s_kv + bf * (K_BYTES + V_BYTES); };
-  auto s_v = [&](int bf) { return s_kv + bf * (K_BYTES + V_BYTES) + K_BYTES; };
+  // K tiles are double-buffered (tile it+1 is requested as soon as S(it) has been issued); V has ONE buffer, requested
+  // when the previous P V has finished and hidden behind S and the softmax of its own tile: 99 KB at 128-wide heads,
+  // so that two CTAs share an SM and overlap each other's load -> MMA -> softmax -> MMA chains
+  const uint32_t s_q = base, s_k0 = s_q + Q_BYTES, s_vb = s_k0 + 2 * K_BYTES, s_p = s_vb + V_BYTES;
+  auto s_k = [&](int bf) { return s_k0 + bf * K_BYTES; };
   const uint32_t bars = s_p + P_BYTES;
   const uint32_t bar_q = bars, bar_kv0 = bars + 8, bar_s = bars + 16, bar_sfree = bars + 24, bar_p = bars + 32,
-                 bar_o = bars + 40, bar_kv1 = bars + 48, tmem_slot = bars + 56;
+                 bar_o = bars + 40, bar_kv1 = bars + 48, bar_v = bars + 56, tmem_slot = bars + 64;
   auto bar_kv = [&](int bf) { return bf ? bar_kv1 : bar_kv0; };
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
   uint8_t* p_ptr = smem_raw + (s_p - smem_u32(smem_raw));
@@ -81,7 +83,7 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 
   if (warp == 1 && lane == 0) {
     mbar_init(bar_q, 1); mbar_init(bar_kv0, 1); mbar_init(bar_kv1, 1); mbar_init(bar_s, 1); mbar_init(bar_sfree, 128);
-    mbar_init(bar_p, 128); mbar_init(bar_o, 1);
+    mbar_init(bar_p, 128); mbar_init(bar_o, 1); mbar_init(bar_v, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -108,15 +110,18 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     for (int kb = 0; kb < KB; ++kb)
       tma_load_2d(s_q + kb * (WQ * 128), &map_q, bar_q, h * p.dim + kb * 64, row0);
     const int total = 2 * n_tiles;
-    auto request = [&](int i) {   // K (and V in pass 1) of flat step i into buffer i & 1
+    auto request = [&](int i) {   // K of flat step i into K buffer i & 1
       const int pass = i >= n_tiles ? 1 : 0, t = t_lo + (pass ? i - n_tiles : i), bf = i & 1;
       const int row = pt_row[t] * WK;
-      mbar_expect_tx(bar_kv(bf), pass == 1 ? K_BYTES + V_BYTES : K_BYTES);
+      mbar_expect_tx(bar_kv(bf), K_BYTES);
       for (int kb = 0; kb < KB; ++kb)
         tma_load_2d(s_k(bf) + kb * (WK * 128), &map_k, bar_kv(bf), kvh * p.dim + kb * 64, row);
-      if (pass == 1)
-        for (int vb = 0; vb < VB; ++vb)
-          tma_load_2d(s_v(bf) + vb * (WK * 128), &map_v, bar_kv(bf), kvh * p.vdim + vb * 64, row);
+    };
+    auto request_v = [&](int t) {   // V of key tile t (pass 1) into the V buffer
+      const int row = pt_row[t_lo + t] * WK;
+      mbar_expect_tx(bar_v, V_BYTES);
+      for (int vb = 0; vb < VB; ++vb)
+        tma_load_2d(s_vb + vb * (WK * 128), &map_v, bar_v, kvh * p.vdim + vb * 64, row);
     };
     request(0);
     if (!wait_lim(bar_q, 0, fail)) goto issuer_done;
@@ -124,6 +129,7 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const int pass = it >= n_tiles ? 1 : 0, t = pass ? it - n_tiles : it, bf = it & 1;
       if (it > 0 && !wait_lim(bar_sfree, (it - 1) & 1, fail)) goto issuer_done;          // S of the previous tile was read
       if (pass == 1 && t > 0 && !wait_lim(bar_o, (t - 1) & 1, fail)) goto issuer_done;   // previous PV done with V and P
+      if (pass == 1) request_v(t);                                 // lands behind S(it) and the softmax of this tile
       if (!wait_lim(bar_kv(bf), (it >> 1) & 1, fail)) goto issuer_done;
       tc_fence_after();
       for (int ks = 0; ks < p.dim / 16; ++ks) {                    // S = Q K^T
@@ -131,12 +137,13 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         umma(tmem_base + S_COL, umma_desc(s_q + off_q), umma_desc(s_k(bf) + off_k), idesc_s, ks > 0 ? 1u : 0u);
       }
       umma_commit(bar_s);
-      if (it + 1 < total) request(it + 1);                         // the other buffer is free (see the waits above)
+      if (it + 1 < total) request(it + 1);                         // the other K buffer is free (bar_sfree above)
       if (pass == 1) {
         if (!wait_lim(bar_p, t & 1, fail)) goto issuer_done;       // P tile is in shared memory
+        if (!wait_lim(bar_v, t & 1, fail)) goto issuer_done;       // and so is V
         tc_fence_after();
         for (int ks = 0; ks < WK / 16; ++ks) {                     // O += P V
-          umma(tmem_base + O_COL, umma_desc(s_p + ks * 32), umma_desc_mn_w(s_v(bf) + ks * 2048, WK * 128), idesc_o,
+          umma(tmem_base + O_COL, umma_desc(s_p + ks * 32), umma_desc_mn_w(s_vb + ks * 2048, WK * 128), idesc_o,
                (t > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(bar_o);
@@ -266,8 +273,8 @@ extern "C" int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int 
              "attention_ragged_tc: cuTensorMapEncodeTiled failed");
   tc::WinParams p = {out, ld_out, gate, ld_gate, tiles, page_table, pt_stride, n_heads, n_heads / n_kv_heads, dim, vdim,
                      scale, window, slopes, err_flag};
-  const size_t smem = 1024 + (size_t)tc::WQ * dim * 2 + 2 * ((size_t)tc::WK * dim * 2 + (size_t)tc::WK * vdim * 2) +
-                      (size_t)tc::WQ * tc::WK * 2 + 64 + 16;
+  const size_t smem = 1024 + (size_t)tc::WQ * dim * 2 + 2 * (size_t)tc::WK * dim * 2 + (size_t)tc::WK * vdim * 2 +
+                      (size_t)tc::WQ * tc::WK * 2 + 72 + 16;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(n_tiles, n_heads);
   if (bf) {
