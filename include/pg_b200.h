@@ -299,6 +299,58 @@ int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int ld_q, const
                            int n_kv_heads, int dim, int vdim, float scale, int window, const float* slopes,
                            int* err_flag, int dtype, void* stream);
 
+/* The same with three extensions.  keep_first > 0: positions < keep_first of the sequence stay visible behind the
+ * window (at their true positions).  sigmoid_weights != 0: no softmax; the weight of a visible key is
+ * sigmoid(score + head_bias[h]) (head_bias: device float[n_heads] or NULL, also added under the softmax) and the
+ * weights are not normalised.  gate_per_head != 0: gate holds one value per (token, head) at gate[t * ld_gate + h]
+ * instead of one per output column.  The result is multiplied by out_scale before it is rounded. */
+int pg_attention_ragged_ex(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                           int gate_per_head, const void* k_pool, const void* v_pool, const int32_t* page_table,
+                           int pt_stride, int page_size, const int32_t* tok_slot, const int32_t* tok_pos,
+                           int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim, float scale, int window,
+                           int keep_first, const float* slopes, int sigmoid_weights, const float* head_bias,
+                           float out_scale, float* ws, long long ws_floats, int dtype, void* stream);
+
+/* Bias, rotary positions, value mixing and cache append for one fused projection row per token: proj row holds
+ * n_heads query heads and n_kv_heads key heads of `dim` columns and n_kv_heads value heads of `vdim` columns at the
+ * given offsets.  Biases (model dtype, may be NULL) are added first.  The first rot_dims columns of every query and
+ * key head are rotated in pairs ((2i, 2i+1) when interleaved != 0, else (i, i + rot_dims/2)) by the angle
+ * position * freq[i] (freq: device float[rot_dims / 2]), cos and sin both multiplied by mag; fp32 angles.  v_first != NULL: the value row
+ * becomes (1 - lambda) v + lambda v_first[t] (row stride ld_vf) before it is cached.  Queries go to q_out (packed),
+ * keys and values to the paged pools at (tok_slot, tok_pos). */
+int pg_rotary_append(void* q_out, const void* proj, int ld, int q_col0, int n_heads, int k_col0, int n_kv_heads,
+                     int dim, int v_col0, int vdim, const void* q_bias, const void* k_bias, const void* v_bias,
+                     const float* freq, int rot_dims, float mag, int interleaved, const void* v_first, int ld_vf,
+                     float lambda, void* k_pool, void* v_pool, const int32_t* page_table, int pt_stride,
+                     int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens, int dtype,
+                     void* stream);
+
+/* Output norm of a sublayer + layer scale + residual sum + the next input norm:
+ * x[r] += scale (.) (y[r] / sqrt(mean(y[r]^2) + eps) * w_post)   (scale: per channel, may be NULL);
+ * out != NULL: out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * w_next (model dtype, packed).  x is the fp32 stream. */
+int pg_postnorm_residual(void* out, float* x, const void* y, int ldy, const void* w_post, const void* scale,
+                         const void* w_next, int rows, int D, float eps, int dtype, void* stream);
+
+/* ---- recurrent mixers: generalised delta rule ---------------------------------------------------------------------
+ * Per head, state S [dim x dim] in fp32 per sequence slot ([slots][heads][dim][dim]):
+ *   u = k / sqrt(sum(k^2) + key_eps);  S <- diag(w) S - (a * u)(u^T S) + k v^T;  o = S^T r.
+ * pg_delta_prep: from the fused projection row (k at k_col0, the removal gate's pre-activation at a_col0, the decay's
+ *   inner projection of width `lora` at lora_col0): decay = exp(-decay_scale * sigmoid(W2 tanh(inner) + w0)) with W2
+ *   [heads * dim, lora], unit = u, rem = sigmoid(a + a_bias) * u; all fp32 [n_tokens, heads * dim].
+ * pg_delta_rule: segs (device int32 [n_segs][3] = {state slot, first token row, tokens}; consecutive rows of one
+ *   sequence in order; 0 tokens: skipped) are advanced from the slot's state, which is updated in place; r, k, v are
+ *   read from the projection row; out fp32 [n_tokens, heads * dim].
+ * pg_headnorm_gate: out[t, h*dim + c] = o / sqrt(mean_h(o^2) + eps) * w[h*dim + c] * sigmoid(gate[t, h*dim + c]) *
+ *   out_scale, rounded to the model dtype (w, gate may be NULL). */
+int pg_delta_prep(float* decay, float* unit, float* rem, const void* proj, int ld, int k_col0, int a_col0,
+                  int lora_col0, int lora, const void* w2, const void* w0, const void* a_bias, int n_tokens, int heads,
+                  int dim, float decay_scale, float key_eps, int dtype, void* stream);
+int pg_delta_rule(float* out, float* state, const void* proj, int ld, int r_col0, int k_col0, int v_col0,
+                  const float* decay, const float* unit, const float* rem, const int32_t* segs, int n_segs, int heads,
+                  int dim, int dtype, void* stream);
+int pg_headnorm_gate(void* out, int ld_out, const float* o, const void* w, const void* gate, int ld_gate, int n_tokens,
+                     int heads, int dim, float eps, float out_scale, int dtype, void* stream);
+
 /* xIELU: z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2;  (p, q) = pq[0..1] in
  * the model dtype.  out may alias z. */
 int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, void* stream);
@@ -306,6 +358,8 @@ int pg_xielu(void* out, const void* z, const void* pq, long long n, int dtype, v
 /* out[r, c] = silu(gate_up[r, c]) * gate_up[r, F + c] for a [rows, 2F] matrix (model dtype): the pairing of a stacked
  * gate/up projection that was computed without it (the weight-streaming kernels of decode-sized steps). */
 int pg_swiglu(void* out, const void* gate_up, int rows, int F, int dtype, void* stream);
+/* The same pairing with the tanh form of GELU on the gate: out = gelu_tanh(gate) * up. */
+int pg_geglu(void* out, const void* gate_up, int rows, int F, int dtype, void* stream);
 
 /* ---- mixture of experts ---------------------------------------------------------------------------------------
  * pg_moe_route: z = h W_router^T in fp32, s = softmax(z) over all n_route outputs, the `top` largest of

@@ -7,6 +7,12 @@
 // decoded token are the same case.  score = (q . k_j) * scale - slope[h] * (p - j); fp32 scores, softmax weights and
 // accumulation; out = softmax(score) V, times sigmoid(gate) when a gate is given, rounded once to the model dtype.
 //
+// Extensions (pg_attention_ragged_ex): keep_first > 0 keeps the first keep_first positions of the sequence visible
+// behind the window (they keep their true positions); the visible keys of a token are then the virtual list
+// [0, min(keep_first, lo)) ++ [lo, p], which every kernel below walks through one index map.  weights == 1 replaces
+// the softmax by unnormalised weights sigmoid(score + head_bias[h]).  The gate is either one value per output column
+// (gate_per_head == 0) or one per (token, head); the result is multiplied by out_scale before the single rounding.
+//
 // attention_ragged_kernel: one warp per (token, head).  32 keys per iteration, one key per lane for the dot
 // product (the query row lives in shared memory as fp32), running (max, sum) rescaling, then the lanes switch to the
 // value columns and walk the 32 keys with the weights broadcast by shuffles.  Warps of a CTA are the heads of the
@@ -85,31 +91,55 @@ struct RagAttnParams {
   int n_tokens, H, G, dim, vdim;
   float scale; int window;
   const float* slopes;
+  int keep_first;                // positions < keep_first stay visible behind the window
+  int sigmoid_weights;           // 0: softmax over the visible keys; 1: weight = sigmoid(score + head_bias[h])
+  const float* head_bias;        // per query head, added to the score (NULL: none)
+  int gate_per_head;             // 0: gate[t][h * vdim + c]; 1: gate[t][h]
+  float out_scale;
+};
+
+// The visible keys of a token at position pos as one list: n_keep kept first positions, then [lo, pos].
+struct KeyRange {
+  int lo, n_keep, count;
+  __device__ __forceinline__ KeyRange(int pos, int window, int keep_first) {
+    lo = window > 0 ? max(0, pos - window + 1) : 0;
+    n_keep = min(max(keep_first, 0), lo);
+    count = n_keep + pos - lo + 1;
+  }
+  __device__ __forceinline__ int key(int v) const { return v < n_keep ? v : lo + (v - n_keep); }
 };
 
 // Process keys [lo, hi] (inclusive) of one (token, head) for the calling warp; (m, l, acc) are the running state.
 template <typename T, int DPL>
 __device__ __forceinline__ void attend_range(const RagAttnParams& p, const float* qs, const int32_t* pt_row, int g,
-                                             int pos, float slope, int lo, int hi, float& m, float& l, float* acc) {
+                                             int pos, float slope, float bias, const KeyRange& kr, float& m, float& l,
+                                             float* acc) {
+  const int lo = 0, hi = kr.count - 1;              // virtual key indices
   const int lane = threadIdx.x & 31;
   const T* kpool = reinterpret_cast<const T*>(p.k_pool);
   const T* vpool = reinterpret_cast<const T*>(p.v_pool);
   const int kw = p.G * p.dim, vw = p.G * p.vdim;
   for (int j0 = lo; j0 <= hi; j0 += 32) {
-    const int j = j0 + lane;
-    const bool valid = j <= hi;
+    const bool valid = j0 + lane <= hi;
+    const int j = kr.key(j0 + lane);
     float s = -INFINITY;
     long long row = 0;
     if (valid) {
       row = (long long)pt_row[j / p.page_size] * p.page_size + j % p.page_size;
-      s = dot_row<T>(qs, kpool + row * kw + g * p.dim, p.dim) * p.scale - slope * (float)(pos - j);
+      s = dot_row<T>(qs, kpool + row * kw + g * p.dim, p.dim) * p.scale - slope * (float)(pos - j) + bias;
     }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float corr = expf(m - m_new);            // m == -inf on the first block: exp(-inf) = 0
-    const float pj = valid ? expf(s - m_new) : 0.f;
-    l = l * corr + warp_sum(pj);
+    float m_new = m, pj;
+    if (p.sigmoid_weights) {                       // unnormalised: no running maximum, m stays 0
+      pj = valid ? 1.f / (1.f + expf(-s)) : 0.f;
+      l += warp_sum(pj);
+    } else {
+      m_new = fmaxf(m, warp_max(s));
+      const float corr = expf(m - m_new);          // m == -inf on the first block: exp(-inf) = 0
+      pj = valid ? expf(s - m_new) : 0.f;
+      l = l * corr + warp_sum(pj);
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+      for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+    }
     const int n = min(32, hi - j0 + 1);
     const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16;   // lane = DPL contiguous columns
 #pragma unroll 8
@@ -136,8 +166,10 @@ template <typename T, int DPL>
 __device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, float l, const float* acc) {
   const int lane = threadIdx.x & 31;
   T* o = reinterpret_cast<T*>(p.out) + (size_t)t * p.ld_out + h * p.vdim;
-  const T* gt = p.gate ? reinterpret_cast<const T*>(p.gate) + (size_t)t * p.ld_gate + h * p.vdim : nullptr;
-  const float inv = 1.f / l;
+  const T* gt = (p.gate && !p.gate_per_head) ? reinterpret_cast<const T*>(p.gate) + (size_t)t * p.ld_gate + h * p.vdim : nullptr;
+  float inv = (p.sigmoid_weights ? 1.f : 1.f / l) * p.out_scale;
+  if (p.gate && p.gate_per_head)
+    inv *= 1.f / (1.f + expf(-to_f<T>(reinterpret_cast<const T*>(p.gate)[(size_t)t * p.ld_gate + h])));
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
     const int c = lane * DPL + i;
@@ -164,12 +196,12 @@ __global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) 
   __syncwarp();
   const int pos = p.tok_pos[t];
   const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
-  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-  const float slope = p.slopes ? p.slopes[h] : 0.f;
-  float m = -INFINITY, l = 0.f, acc[DPL];
+  const KeyRange kr(pos, p.window, p.keep_first);
+  const float slope = p.slopes ? p.slopes[h] : 0.f, bias = p.head_bias ? p.head_bias[h] : 0.f;
+  float m = p.sigmoid_weights ? 0.f : -INFINITY, l = 0.f, acc[DPL];
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
-  attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, lo, pos, m, l, acc);
+  attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, bias, kr, m, l, acc);
   store_out<T, DPL>(p, t, h, l, acc);
 }
 
@@ -217,27 +249,31 @@ __global__ void __launch_bounds__(128) attention_ragged_split_kernel(RagAttnPara
   __syncthreads();
   const int pos = p.tok_pos[t];
   const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
-  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-  float slope[R];
+  const KeyRange kr(pos, p.window, p.keep_first);
+  float slope[R], bias[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) slope[r] = p.slopes ? p.slopes[h0 + r] : 0.f;
+  for (int r = 0; r < R; ++r) {
+    slope[r] = p.slopes ? p.slopes[h0 + r] : 0.f;
+    bias[r] = p.head_bias ? p.head_bias[h0 + r] : 0.f;
+  }
   const T* kpool = reinterpret_cast<const T*>(p.k_pool);
   const T* vpool = reinterpret_cast<const T*>(p.v_pool);
   const int kw = p.G * p.dim, vw = p.G * p.vdim;
   const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16;
-  // this CTA's slice of [lo, pos]: whole 32-key blocks
-  const int blocks = (pos - lo + 32) / 32, per = (blocks + gridDim.y - 1) / gridDim.y;
+  // this CTA's slice of the visible keys: whole 32-key blocks
+  const int blocks = (kr.count + 31) / 32, per = (blocks + gridDim.y - 1) / gridDim.y;
   const int b_begin = blockIdx.y * per, b_end = min(blocks, b_begin + per);
   float m[R], l[R], acc[R][DPL];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    m[r] = -INFINITY; l[r] = 0.f;
+    m[r] = p.sigmoid_weights ? 0.f : -INFINITY; l[r] = 0.f;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[r][i] = 0.f;
   }
   for (int b = b_begin + warp; b < b_end; b += warps) {
-    const int j0 = lo + 32 * b, hi = min(pos, j0 + 31), j = j0 + lane;
-    const bool valid = j <= hi;
+    const int j0 = 32 * b, hi = min(kr.count - 1, j0 + 31);
+    const bool valid = j0 + lane <= hi;
+    const int j = kr.key(j0 + lane);
     long long row = 0;
     float s[R], pj[R];
 #pragma unroll
@@ -246,10 +282,15 @@ __global__ void __launch_bounds__(128) attention_ragged_split_kernel(RagAttnPara
       row = (long long)pt_row[j / p.page_size] * p.page_size + j % p.page_size;
       dot_rows<T, R>(qs, p.dim, kpool + row * kw + g * p.dim, s);
 #pragma unroll
-      for (int r = 0; r < R; ++r) s[r] = s[r] * p.scale - slope[r] * (float)(pos - j);
+      for (int r = 0; r < R; ++r) s[r] = s[r] * p.scale - slope[r] * (float)(pos - j) + bias[r];
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
+      if (p.sigmoid_weights) {
+        pj[r] = valid ? 1.f / (1.f + expf(-s[r])) : 0.f;
+        l[r] += warp_sum(pj[r]);
+        continue;
+      }
       const float m_new = fmaxf(m[r], warp_max(s[r]));
       const float corr = expf(m[r] - m_new);
       pj[r] = valid ? expf(s[r] - m_new) : 0.f;
@@ -376,17 +417,20 @@ static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats,
 
 using namespace pg;
 
-extern "C" int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
-                                   const void* k_pool, const void* v_pool, const int32_t* page_table, int pt_stride,
-                                   int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens,
-                                   int n_heads, int n_kv_heads, int dim, int vdim, float scale, int window,
-                                   const float* slopes, float* ws, long long ws_floats, int dtype, void* stream) {
+extern "C" int pg_attention_ragged_ex(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                      int gate_per_head, const void* k_pool, const void* v_pool,
+                                      const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
+                                      const int32_t* tok_pos, int n_tokens, int n_heads, int n_kv_heads, int dim,
+                                      int vdim, float scale, int window, int keep_first, const float* slopes,
+                                      int sigmoid_weights, const float* head_bias, float out_scale, float* ws,
+                                      long long ws_floats, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
   PG_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_ragged: heads %d / kv heads %d",
              n_heads, n_kv_heads);
   PG_REQUIRE(dim > 0 && dim <= 512 && vdim > 0 && vdim <= 256, "attention_ragged: dim %d (<= 512), vdim %d (<= 256)", dim, vdim);
   RagAttnParams p = {out, ld_out, q, ld_q, gate, ld_gate, k_pool, v_pool, page_table, pt_stride, page_size, tok_slot,
-                     tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, slopes};
+                     tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, slopes, keep_first,
+                     sigmoid_weights ? 1 : 0, head_bias, gate_per_head ? 1 : 0, out_scale};
   cudaStream_t st = (cudaStream_t)stream;
   const int dpl = (vdim + 31) / 32;
   PG_DISPATCH_DTYPE(dtype, T, {
@@ -396,4 +440,14 @@ extern "C" int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_
     return launch_ragged<T, 8>(p, ws, ws_floats, st);
   });
   return PG_OK;
+}
+
+extern "C" int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                   const void* k_pool, const void* v_pool, const int32_t* page_table, int pt_stride,
+                                   int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens,
+                                   int n_heads, int n_kv_heads, int dim, int vdim, float scale, int window,
+                                   const float* slopes, float* ws, long long ws_floats, int dtype, void* stream) {
+  return pg_attention_ragged_ex(out, ld_out, q, ld_q, gate, ld_gate, 0, k_pool, v_pool, page_table, pt_stride, page_size,
+                                tok_slot, tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, 0, slopes, 0,
+                                nullptr, 1.f, ws, ws_floats, dtype, stream);
 }

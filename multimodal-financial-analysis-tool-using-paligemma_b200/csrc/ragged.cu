@@ -125,8 +125,10 @@ __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ z, const
   for (long long i = first; i < n; i += stride) out[i] = from_f<T>(act(to_f<T>(z[i])));
 }
 
-// ------------------------------------------------------------------ SwiGLU pairing of a stacked [gate | up] row
-template <typename T>
+// ------------------------------------------------------------------ gated pairing of a stacked [gate | up] row
+// GELU == false: silu(gate) * up; GELU == true: gelu_tanh(gate) * up.  The activation is rounded to the model dtype
+// before the product, as the GEMM epilogues do.
+template <typename T, bool GELU>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int rows, int F) {
   pdl_launch_dependents();
   pdl_wait();
@@ -134,8 +136,105 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F, c = i % F;
     const float g = to_f<T>(gu[r * 2 * F + c]), u = to_f<T>(gu[r * 2 * F + F + c]);
-    out[i] = from_f<T>(rnd<T>(g / (1.f + expf(-g))) * u);
+    out[i] = from_f<T>(rnd<T>(GELU ? gelu_tanh(g) : g / (1.f + expf(-g))) * u);
   }
+}
+
+
+// ------------------------------------------------------------------ bias + rotary positions + value mixing + cache append
+// One CTA per token.  proj row = [.. q (H heads x dim) .. k (G x dim) .. v (G x vdim) ..] at the given column offsets.
+// Optional biases (model dtype) are added in fp32 first.  The first rot_dims columns of every query and key head are
+// rotated as pairs: interleaved != 0 pairs column 2i with 2i + 1, otherwise column i with i + rot_dims / 2; the pair
+// (a, b) at position p becomes mag * (a cos t - b sin t, b cos t + a sin t) with t = p * freq[i], evaluated in fp32
+// with the full-range sincosf; the other columns pass unchanged.  v_first != NULL: the value row becomes
+// (1 - lambda) v + lambda v_first[t] (the values of the same token from an earlier layer) before it is cached.
+// Query rows go to q_out (packed), key and value rows to the paged pools at (tok_slot, tok_pos).
+template <typename T>
+__global__ void rotary_append_kernel(T* __restrict__ q_out, const T* __restrict__ proj, int ld, int q_col0, int H,
+                                     int k_col0, int G, int dim, int v_col0, int vdim, const T* __restrict__ q_bias,
+                                     const T* __restrict__ k_bias, const T* __restrict__ v_bias,
+                                     const float* __restrict__ freq, int rot_dims, float mag, int interleaved,
+                                     const T* __restrict__ v_first, int ld_vf, float lambda, T* __restrict__ k_pool,
+                                     T* __restrict__ v_pool, const int32_t* __restrict__ page_table, int pt_stride,
+                                     int page_size, const int32_t* __restrict__ tok_slot,
+                                     const int32_t* __restrict__ tok_pos) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const T* row = proj + (size_t)t * ld;
+  const int p = tok_pos[t];
+  const float fp = (float)p;
+  const size_t slot_row = (size_t)page_table[(size_t)tok_slot[t] * pt_stride + p / page_size] * page_size + p % page_size;
+  T* kdst = k_pool + slot_row * ((size_t)G * dim);
+  T* qdst = q_out + (size_t)t * H * dim;
+  const int half = rot_dims >> 1, rest = dim - rot_dims;
+  // rotated pairs of the query heads, then of the key heads
+  for (int idx = threadIdx.x; idx < (H + G) * half; idx += blockDim.x) {
+    const bool is_k = idx >= H * half;
+    const int li = is_k ? idx - H * half : idx, head = li / half, i = li % half;
+    const int c0 = interleaved ? 2 * i : i, c1 = interleaved ? 2 * i + 1 : i + half;
+    const int base = head * dim;
+    const T* src = row + (is_k ? k_col0 : q_col0) + base;
+    const T* bias = is_k ? k_bias : q_bias;
+    float a = to_f<T>(src[c0]), b = to_f<T>(src[c1]);
+    if (bias) { a += to_f<T>(bias[base + c0]); b += to_f<T>(bias[base + c1]); }
+    float sn, cs;
+    sincosf(fp * freq[i], &sn, &cs);
+    sn *= mag; cs *= mag;
+    T* dst = (is_k ? kdst : qdst) + base;
+    dst[c0] = from_f<T>(a * cs - b * sn);
+    dst[c1] = from_f<T>(b * cs + a * sn);
+  }
+  // columns that are not rotated
+  for (int idx = threadIdx.x; idx < (H + G) * rest; idx += blockDim.x) {
+    const bool is_k = idx >= H * rest;
+    const int li = is_k ? idx - H * rest : idx, c = (li / rest) * dim + rot_dims + li % rest;
+    const T* bias = is_k ? k_bias : q_bias;
+    float a = to_f<T>(row[(is_k ? k_col0 : q_col0) + c]);
+    if (bias) a += to_f<T>(bias[c]);
+    (is_k ? kdst : qdst)[c] = from_f<T>(a);
+  }
+  T* vdst = v_pool + slot_row * ((size_t)G * vdim);
+  const T* vf = v_first ? v_first + (size_t)t * ld_vf : nullptr;
+  for (int c = threadIdx.x; c < G * vdim; c += blockDim.x) {
+    float v = to_f<T>(row[v_col0 + c]);
+    if (v_bias) v += to_f<T>(v_bias[c]);
+    if (vf) v = (1.f - lambda) * v + lambda * to_f<T>(vf[c]);
+    vdst[c] = from_f<T>(v);
+  }
+}
+
+// ------------------------------------------------------------------ output norm + layer scale + residual sum + next input norm
+// One warp per row.  x[r] += scale (.) (y[r] / sqrt(mean(y[r]^2) + eps) * w_post) with y a sublayer's output (model
+// dtype), w_post its output-norm weight and `scale` a per-channel layer scale (NULL: none); then, when out != NULL,
+// out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * w_next: the next sublayer's input.  Statistics and sums in fp32.
+template <typename T>
+__global__ void postnorm_residual_kernel(T* __restrict__ out, float* __restrict__ x, const T* __restrict__ y, int ldy,
+                                         const T* __restrict__ w_post, const T* __restrict__ scale,
+                                         const T* __restrict__ w_next, int rows, int D, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const T* yr = y + (size_t)r * ldy;
+  float* xr = x + (size_t)r * D;
+  float ss = 0.f;
+  for (int c = lane; c < D; c += 32) { const float v = to_f<T>(yr[c]); ss += v * v; }
+  ss = warp_sum(ss);
+  const float inv_y = 1.f / sqrtf(ss / (float)D + eps);
+  float sx = 0.f;
+  for (int c = lane; c < D; c += 32) {
+    float v = to_f<T>(yr[c]) * inv_y * to_f<T>(w_post[c]);
+    if (scale) v *= to_f<T>(scale[c]);
+    v += xr[c];
+    xr[c] = v;
+    sx += v * v;
+  }
+  if (!out) return;
+  sx = warp_sum(sx);
+  const float inv_x = 1.f / sqrtf(sx / (float)D + eps);
+  T* o = out + (size_t)r * D;
+  for (int c = lane; c < D; c += 32) o[c] = from_f<T>(xr[c] * inv_x * to_f<T>(w_next[c]));
 }
 
 }  // namespace pg
@@ -204,8 +303,56 @@ extern "C" int pg_swiglu(void* out, const void* gate_up, int rows, int F, int dt
   const long long n = (long long)rows * F;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   PG_DISPATCH_DTYPE(dtype, T, {
-    return launch_pdl("swiglu", swiglu_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+    return launch_pdl("swiglu", swiglu_kernel<T, false>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
                       (const T*)gate_up, rows, F);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_geglu(void* out, const void* gate_up, int rows, int F, int dtype, void* stream) {
+  if (rows <= 0 || F <= 0) return PG_OK;
+  const long long n = (long long)rows * F;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  PG_DISPATCH_DTYPE(dtype, T, {
+    return launch_pdl("geglu", swiglu_kernel<T, true>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                      (const T*)gate_up, rows, F);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_rotary_append(void* q_out, const void* proj, int ld, int q_col0, int n_heads, int k_col0,
+                                int n_kv_heads, int dim, int v_col0, int vdim, const void* q_bias, const void* k_bias,
+                                const void* v_bias, const float* freq, int rot_dims, float mag, int interleaved,
+                                const void* v_first, int ld_vf, float lambda, void* k_pool, void* v_pool,
+                                const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
+                                const int32_t* tok_pos, int n_tokens, int dtype, void* stream) {
+  if (n_tokens <= 0) return PG_OK;
+  PG_REQUIRE(k_pool && v_pool && page_table && tok_slot && tok_pos && page_size > 0, "rotary_append: pools and token map");
+  PG_REQUIRE(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq),
+             "rotary_append: %d rotated columns of %d (even, with a frequency table)", rot_dims, dim);
+  PG_DISPATCH_DTYPE(dtype, T, {
+    const int work = (n_heads + n_kv_heads) * dim;
+    const int threads = work >= 4096 ? 512 : (work >= 1024 ? 256 : 128);
+    return launch_pdl("rotary_append", rotary_append_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream,
+                      (T*)q_out, (const T*)proj, ld, q_col0, n_heads, k_col0, n_kv_heads, dim, v_col0, vdim,
+                      (const T*)q_bias, (const T*)k_bias, (const T*)v_bias, freq, rot_dims, mag, interleaved,
+                      (const T*)v_first, ld_vf, lambda, (T*)k_pool, (T*)v_pool, page_table, pt_stride, page_size,
+                      tok_slot, tok_pos);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_postnorm_residual(void* out, float* x, const void* y, int ldy, const void* w_post,
+                                    const void* scale, const void* w_next, int rows, int D, float eps, int dtype,
+                                    void* stream) {
+  if (rows <= 0) return PG_OK;
+  PG_REQUIRE(x && y && w_post && ldy >= D, "postnorm_residual: x, y and the output-norm weight are needed");
+  PG_REQUIRE(!out || w_next, "postnorm_residual: a normalised output needs a weight");
+  const int warps = 8;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    return launch_pdl("postnorm_residual", postnorm_residual_kernel<T>, dim3(cdiv(rows, warps)), dim3(warps * 32), 0,
+                      (cudaStream_t)stream, (T*)out, x, (const T*)y, ldy, (const T*)w_post, (const T*)scale,
+                      (const T*)w_next, rows, D, eps);
   });
   return PG_OK;
 }

@@ -73,6 +73,15 @@ SIGNATURES = {
                                _vp, _vp, _i, _vp],
     "pg_xielu": [_vp, _vp, _vp, _ll, _i, _vp],
     "pg_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "pg_geglu": [_vp, _vp, _i, _i, _i, _vp],
+    "pg_attention_ragged_ex": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
+                               _i, _vp, _i, _vp, _f, _vp, _ll, _i, _vp],
+    "pg_rotary_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _i, _vp, _i, _f, _vp, _vp,
+                         _vp, _i, _i, _vp, _vp, _i, _i, _vp],
+    "pg_postnorm_residual": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _i, _vp],
+    "pg_delta_prep": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f, _i, _vp],
+    "pg_delta_rule": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pg_headnorm_gate": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _vp],
     "pg_moe_route": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "pg_moe_sort": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "pg_moe_gemm": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],

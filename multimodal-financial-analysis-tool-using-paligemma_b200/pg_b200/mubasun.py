@@ -31,7 +31,7 @@ import torch
 
 from . import _cabi as cabi
 from ._cabi import ptr
-from .pool import PagePool
+from .ragged_engine import RaggedEngine, StepInputs
 from .registry import register
 
 
@@ -122,45 +122,25 @@ def distance_slopes(heads: int) -> torch.Tensor:
 
 
 @register("Mubasun")
-class MubasunEngine(PagePool):
+class MubasunEngine(RaggedEngine):
     """Weights + paged pools + the launch sequence of one step over a ragged token batch."""
 
-    ragged = True                    # served by scheduler.RaggedBatcher
+    _ERR_TEXT = {2: "the grouped expert GEMM gave up waiting on its pipeline (its results are invalid)"}
 
     def __init__(self, config, weights: Mapping[str, torch.Tensor], *, device="cuda", dtype=torch.bfloat16,
                  page_size: int = 64, kv_pool_tokens: int = 65536, gemm_impl: int = 0, moe_impl: int = 0):
-        cabi.lib()                   # fail now if the CUDA library is missing
         self.cfg = config if isinstance(config, MubasunConfig) else MubasunConfig.from_dict(config)
-        self.device = torch.device(device)
-        if self.device.type != "cuda":
-            raise RuntimeError("pg_b200 runs on CUDA devices only (no CPU fallback)")
-        if dtype not in (torch.bfloat16, torch.float32):
-            raise RuntimeError(f"unsupported model dtype {dtype} (bfloat16 or float32)")
-        self.dtype, self.dt = dtype, cabi.DTYPE_CODE[dtype]
-        self.vec = 4 if dtype == torch.float32 else 8
-        self.page_size = int(page_size)
-        self.gemm_impl = int(os.environ.get("PG_RAGGED_GEMM_IMPL", gemm_impl))
+        self._init_common(device=device, dtype=dtype, page_size=page_size, gemm_impl=gemm_impl)
+        self.max_positions = self.cfg.max_positions
         self.moe_impl = int(os.environ.get("PG_MOE_IMPL", moe_impl))
-        self.small_m_gemv = os.environ.get("PG_RAGGED_GEMV", "1") != "0"
-        # rows up to which a projection streams its weights through the GEMV kernel; from there on the 16-bit path
-        # takes the tensor-core GEMMs (the GEMV turns ALU-bound as rows are added), fp32 keeps it to its 8-row limit
-        self.gemv_max_rows = cabi.MAX_DECODE_BATCH if dtype == torch.float32 else max(1, cabi.BATCHED_DECODE_MIN - 1)
         self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "1"))
-        # steps of up to this many tokens (decode steps, short portions) replay a CUDA graph captured per token count
-        self.graph_max_tokens = int(os.environ.get("PG_RAGGED_GRAPH_TOKENS", "16"))
-        # steps of at least this many tokens run the tcgen05 attention kernel (layers whose head sizes it takes)
-        self.attn_tc_min_tokens = int(os.environ.get("PG_RAGGED_ATTN_TC_MIN", "48"))
-        self._graphs: Dict[tuple, tuple] = {}
-        self._op_timing = os.environ.get("PG_OP_TIMING", "0") == "1"
-        self._op_events: List[tuple] = []
         self._repack(weights)
         for w, lc in zip(self.layers, self.cfg.layers):
             npj = w["proj"].shape[0]
             w["attn_tc"] = bool(cabi.lib().pg_attention_ragged_tc_ok(lc.mixer.dim, lc.mixer.vdim, self.page_size, w["nq"],
                                                                      w["ng"], npj, self.dt)) and w["g_col"] % 8 == 0
         self._attn_tc_any = any(w["attn_tc"] for w in self.layers)
-        # +1: the scheduler parks the unused page-table entries on a page of their own
-        self._init_pool((int(kv_pool_tokens) + self.page_size - 1) // self.page_size + 1)
+        self._init_runtime(kv_pool_tokens)
         self.k_pools: Dict[int, torch.Tensor] = {}
         self.v_pools: Dict[int, torch.Tensor] = {}
         for i, L in enumerate(self.cfg.layers):
@@ -170,21 +150,6 @@ class MubasunEngine(PagePool):
                                               device=self.device)
                 self.v_pools[i] = torch.zeros((self.num_pages, self.page_size, m.kv_heads * m.vdim), dtype=dtype,
                                               device=self.device)
-        self.err_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self._err_np = self.err_flag.numpy()
-        self.attn_ws = torch.empty(5 << 19, dtype=torch.float32, device=self.device)   # key-slice partials of decode steps
-        if dtype != torch.float32:   # scratch of the split-K prompt GEMMs (shared with the other engines)
-            from .engine import _WORKSPACES
-            key = (self.device.index,)
-            if key not in _WORKSPACES:
-                _WORKSPACES[key] = torch.empty(int(os.environ.get("PG_WORKSPACE_MB", "80")) << 20, dtype=torch.uint8,
-                                               device=self.device)
-            ws = _WORKSPACES[key]
-            cabi.check(cabi.lib().pg_set_workspace(ptr(ws), ws.numel()), "set_workspace")
-
-    @classmethod
-    def from_checkpoint(cls, config, tensors, *, device="cuda", dtype=torch.bfloat16, **kw):
-        return cls(config, tensors, device=device, dtype=dtype, **kw)
 
     # ------------------------------------------------------------------ weights
     def _repack(self, weights: Mapping[str, torch.Tensor]) -> None:
@@ -240,33 +205,6 @@ class MubasunEngine(PagePool):
             raise ValueError(f"checkpoint holds {len(extra)} tensor(s) the config does not describe: {extra[:5]}")
 
     # ------------------------------------------------------------------ op wrappers
-    def _new(self, *shape, dtype=None):
-        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
-
-    def _linear(self, a: torch.Tensor, w: torch.Tensor, epi: int = cabi.EPI_NONE, out_f32: bool = False) -> torch.Tensor:
-        """out = a w^T (+ the gated pairing of stacked [Wg; Wu] weights), rounded to the model dtype."""
-        M, K = a.shape
-        N = w.shape[0] // 2 if epi in (cabi.EPI_GEGLU, cabi.EPI_SWIGLU) else w.shape[0]
-        out = self._new(M, N, dtype=torch.float32 if out_f32 else None)
-        L, st = cabi.lib(), cabi.stream()
-        if self.small_m_gemv and M <= self.gemv_max_rows and K % self.vec == 0 and a.is_contiguous():
-            # a handful of rows (decode steps): the weight-streaming GEMV kernel of the decode path; the gated pairing
-            # and the fp32 copy of the logits (rounded to the model dtype first, as the GEMM epilogue does) follow
-            if epi == cabi.EPI_NONE:
-                tmp = self._new(M, N) if out_f32 else out
-                cabi.check(L.pg_gemv_res(ptr(tmp), ptr(a), ptr(w), None, M, N, K, None, self.dt, st), "gemv")
-                if out_f32:
-                    out.copy_(tmp)
-                return out
-            if epi == cabi.EPI_SWIGLU and not out_f32:
-                gu = self._new(M, 2 * N)
-                cabi.check(L.pg_gemv_res(ptr(gu), ptr(a), ptr(w), None, M, 2 * N, K, None, self.dt, st), "gemv")
-                cabi.check(L.pg_swiglu(ptr(out), ptr(gu), M, N, self.dt, st), "swiglu")
-                return out
-        cabi.check(L.pg_gemm(ptr(out), ptr(a), ptr(w), None, None, M, N, K, a.stride(0), w.stride(0), out.stride(0), 0, 0,
-                             epi, 1 if out_f32 else 0, self.gemm_impl, self.dt, st), "gemm")
-        return out
-
     def _norm(self, out, x, w, add_a=None, add_b=None, rows_idx=None, rows=None):
         c = self.cfg
         n = x.shape[0] if rows is None else rows
@@ -276,74 +214,11 @@ class MubasunEngine(PagePool):
             cabi.stream()), "group_rmsnorm")
 
     # ------------------------------------------------------------------ one step
-    @torch.no_grad()
-    def forward_tokens(self, kv, ids: Sequence[int], slots: Sequence[int], positions: Sequence[int],
-                       want_rows: Sequence[int], layer_sink: Optional[list] = None) -> torch.Tensor:
-        """Run the listed tokens (token t: id, page-table row of its sequence, position in it) through the model
-        from the cache that earlier steps left, append their keys and values, and return the fp32 logits
-        [len(want_rows), vocab] of the listed rows.  `kv` is the scheduler's slot table; its pages for the new
-        positions must be reserved (SlotKV.ensure).  layer_sink (debugging): receives the residual stream after
-        every layer."""
-        c = self.cfg
-        T, nw = len(ids), len(want_rows)
-        if T == 0:
-            return torch.empty((0, c.vocab), dtype=torch.float32, device=self.device)
-        if max(positions) >= c.max_positions:
-            raise ValueError(f"position {max(positions)} exceeds max_positions {c.max_positions}")
-        # query tiles of the tensor-core attention: runs of <= 128 consecutive tokens of one sequence
-        tiles: List[int] = []
-        if T >= self.attn_tc_min_tokens and self._attn_tc_any:
-            t0 = 0
-            while t0 < T:
-                t1 = t0 + 1
-                while t1 < T and t1 - t0 < 128 and slots[t1] == slots[t0] and positions[t1] == positions[t1 - 1] + 1:
-                    t1 += 1
-                tiles += [t0, t1 - t0, int(slots[t0]), int(positions[t0])]
-                t0 = t1
-        nt = len(tiles) // 4
-        host = torch.empty(4 * T + nw + 4 * nt, dtype=torch.int32).pin_memory()   # ids (int64) | slot | pos | want | tiles
-        if nt:
-            host[4 * T + nw:].copy_(torch.as_tensor(tiles, dtype=torch.int32))
-        host[:2 * T].view(torch.int64).copy_(torch.as_tensor(ids, dtype=torch.int64))
-        host[2 * T:3 * T].copy_(torch.as_tensor(slots, dtype=torch.int32))
-        host[3 * T:4 * T].copy_(torch.as_tensor(positions, dtype=torch.int32))
-        if nw:
-            host[4 * T:4 * T + nw].copy_(torch.as_tensor(want_rows, dtype=torch.int32))
-        if (T <= self.graph_max_tokens and layer_sink is None and not self._op_timing
-                and not torch.cuda.is_current_stream_capturing()):
-            return self._replay(kv, host, T, nw)
-        return self._forward_device(kv, host.to(self.device, non_blocking=True), T, nw, layer_sink)
-
-    def _replay(self, kv, host: torch.Tensor, T: int, nw: int) -> torch.Tensor:
-        """Small steps are launch-bound (some fifteen launches per layer): the kernel sequence for (T tokens, nw
-        wanted rows) over this slot table is captured once; a step copies its ids / slots / positions into the
-        graph's static input and replays.  Which kernels run depends on the counts only, never on the values."""
-        key = (T, nw, kv.page_table.data_ptr(), kv.max_pages)
-        ent = self._graphs.get(key)
-        if ent is None:
-            static_in = torch.zeros(4 * T + nw, dtype=torch.int32, device=self.device)
-            static_in.copy_(host, non_blocking=True)
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):          # warm-up outside the capture (module loading, shared-memory attributes)
-                self._forward_device(kv, static_in, T, nw, None)
-            torch.cuda.current_stream().wait_stream(s)
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                out = self._forward_device(kv, static_in, T, nw, None)
-            ent = self._graphs[key] = (g, static_in, out)
-            if len(self._graphs) > 64:
-                self._graphs.pop(next(iter(self._graphs)))
-        g, static_in, out = ent
-        static_in.copy_(host, non_blocking=True)
-        g.replay()
-        return out.clone()
-
-    def _forward_device(self, kv, dev: torch.Tensor, T: int, nw: int, layer_sink: Optional[list]) -> torch.Tensor:
+    def _forward_device(self, kv, inp: StepInputs, layer_sink: Optional[list]) -> torch.Tensor:
         c, L, st = self.cfg, cabi.lib(), cabi.stream()
         tm = self._tm
-        d_ids, d_slot, d_pos, d_want = dev[:2 * T].view(torch.int64), dev[2 * T:3 * T], dev[3 * T:4 * T], dev[4 * T:4 * T + nw]
-        d_tiles, n_qt = dev[4 * T + nw:], (dev.numel() - 4 * T - nw) // 4
+        T, nw = inp.T, inp.nw
+        d_ids, d_slot, d_pos, d_want, d_tiles, n_qt = inp.ids, inp.slot, inp.pos, inp.want, inp.tiles, inp.n_tiles
         D = c.width
         x = self._new(T, D, dtype=torch.float32)
         cabi.check(L.pg_embed_pos(ptr(x), ptr(d_ids), ptr(d_pos), ptr(self.emb), ptr(self.pos), T, D, c.vocab,
@@ -451,38 +326,6 @@ class MubasunEngine(PagePool):
             cabi.check(L.pg_moe_combine(ptr(x), ptr(y), D, ptr(pos), ptr(wts), ptr(h), h.stride(0), ptr(so),
                                         0 if so is None else so.stride(0), ptr(sg), T, D, ml.top, self.dt, st),
                        "moe_combine")
-
-    # ------------------------------------------------------------------ per-op timing (diagnostic: PG_OP_TIMING=1)
-    def _tm(self, name):
-        """CUDA-event bracket around one op when op timing is on (durations inside the real step, with the L2 state
-        of the real step); `op_times()` sums them per name.  A no-op otherwise."""
-        from .engine import PaliGemmaEngine
-        if not self._op_timing:
-            return PaliGemmaEngine._NoTimer()
-        return PaliGemmaEngine._EvTimer(self._op_events, name)
-
-    def op_times(self, reset: bool = True) -> Dict[str, float]:
-        torch.cuda.synchronize()
-        out: Dict[str, float] = {}
-        for name, e0, e1 in self._op_events:
-            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
-        if reset:
-            self._op_events = []
-        return out
-
-    # ------------------------------------------------------------------ serving glue
-    def new_batcher(self, **kw):
-        from .scheduler import RaggedBatcher
-        return RaggedBatcher(self, **kw)
-
-    def check_errors(self, sync: bool = False) -> None:
-        if sync:
-            torch.cuda.current_stream(self.device).synchronize()
-        if self._err_np[0] != 0:
-            code, self._err_np[0] = int(self._err_np[0]), 0
-            if code == 2:
-                raise RuntimeError("the grouped expert GEMM gave up waiting on its pipeline (its results are invalid)")
-            raise RuntimeError("a token id lies outside the vocabulary or a position outside max_positions")
 
     def weight_bytes(self) -> int:
         n = sum(t.numel() for t in (self.emb, self.pos, self.final_norm, self.head))

@@ -1,0 +1,266 @@
+"""Common part of the engines that serve decoder-only models on ragged token batches.
+
+A step is a flat token list: token t carries (id, page-table row of its sequence, position in it), so prompt portions
+and single decoded tokens of different sequences share every launch.  This class owns what does not depend on the
+design: the page pool, the host -> device packing of a step's inputs, the CUDA-graph replay of small steps, the
+projection wrapper over the library's GEMM / GEMV kernels, per-op timing and the serving glue.  A design subclasses it
+with its config, its weight repacking (`_repack`), its caches and its launch sequence (`_forward_device`).
+
+Inputs of a step on the device (one int32 buffer, `StepInputs` names its parts):
+
+    ids (int64) | page-table row | position | wanted rows | segments | query tiles
+
+* segments (engines with `needs_segments`: recurrent state per sequence slot): {slot, first token row, tokens} for
+  every run of consecutive tokens of one sequence, padded with empty segments to min(tokens, slots) entries so that a
+  captured launch sequence depends on the token count only;
+* query tiles (steps of at least `attn_tc_min_tokens` tokens on engines whose attention has a tensor-core kernel):
+  {first token row, rows, page-table row, first position} for runs of up to 128 consecutive tokens of one sequence.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from . import _cabi as cabi
+from ._cabi import ptr
+from .pool import PagePool
+
+
+@dataclass
+class StepInputs:
+    T: int
+    nw: int
+    ids: torch.Tensor            # int64 [T]
+    slot: torch.Tensor           # int32 [T]
+    pos: torch.Tensor            # int32 [T]
+    want: torch.Tensor           # int32 [nw]
+    segs: torch.Tensor           # int32 [3 * n_segs]
+    n_segs: int
+    tiles: torch.Tensor          # int32 [4 * n_tiles]
+    n_tiles: int
+
+
+class RaggedEngine(PagePool):
+    """Weights + paged pools + the launch sequence of one step over a ragged token batch."""
+
+    ragged = True                    # served by scheduler.RaggedBatcher
+    needs_segments = False           # the step needs the per-sequence runs of its tokens (recurrent state)
+    max_positions: Optional[int] = None   # longest sequence the design can address (None: no bound of its own)
+
+    def _init_common(self, *, device, dtype, page_size: int, gemm_impl: int = 0) -> None:
+        cabi.lib()                   # fail now if the CUDA library is missing
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("pg_b200 runs on CUDA devices only (no CPU fallback)")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise RuntimeError(f"unsupported model dtype {dtype} (bfloat16 or float32)")
+        self.dtype, self.dt = dtype, cabi.DTYPE_CODE[dtype]
+        self.vec = 4 if dtype == torch.float32 else 8
+        self.page_size = int(page_size)
+        self.gemm_impl = int(os.environ.get("PG_RAGGED_GEMM_IMPL", gemm_impl))
+        self.small_m_gemv = os.environ.get("PG_RAGGED_GEMV", "1") != "0"
+        # rows up to which a projection streams its weights through the GEMV kernel; from there on the 16-bit path
+        # takes the tensor-core GEMMs (the GEMV turns ALU-bound as rows are added), fp32 keeps it to its 8-row limit
+        self.gemv_max_rows = cabi.MAX_DECODE_BATCH if dtype == torch.float32 else max(1, cabi.BATCHED_DECODE_MIN - 1)
+        # steps of up to this many tokens (decode steps, short portions) replay a CUDA graph captured per token count
+        self.graph_max_tokens = int(os.environ.get("PG_RAGGED_GRAPH_TOKENS", "16"))
+        # steps of at least this many tokens run the tcgen05 attention kernel (layers whose head sizes it takes)
+        self.attn_tc_min_tokens = int(os.environ.get("PG_RAGGED_ATTN_TC_MIN", "48"))
+        self._attn_tc_any = False
+        self._graphs: Dict[tuple, tuple] = {}
+        self._op_timing = os.environ.get("PG_OP_TIMING", "0") == "1"
+        self._op_events: List[tuple] = []
+
+    def _init_runtime(self, kv_pool_tokens: int) -> None:
+        """Page pool, error flag, attention scratch and the GEMM workspace (after the weights are in place)."""
+        # +1: the scheduler parks the unused page-table entries on a page of their own
+        self._init_pool((int(kv_pool_tokens) + self.page_size - 1) // self.page_size + 1)
+        self.err_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._err_np = self.err_flag.numpy()
+        self.attn_ws = torch.empty(5 << 19, dtype=torch.float32, device=self.device)   # key-slice partials of decode steps
+        if self.dtype != torch.float32:   # scratch of the split-K prompt GEMMs (shared with the other engines)
+            from .engine import _WORKSPACES
+            key = (self.device.index,)
+            if key not in _WORKSPACES:
+                _WORKSPACES[key] = torch.empty(int(os.environ.get("PG_WORKSPACE_MB", "80")) << 20, dtype=torch.uint8,
+                                               device=self.device)
+            ws = _WORKSPACES[key]
+            cabi.check(cabi.lib().pg_set_workspace(ptr(ws), ws.numel()), "set_workspace")
+
+    @classmethod
+    def from_checkpoint(cls, config, tensors, *, device="cuda", dtype=torch.bfloat16, **kw):
+        return cls(config, tensors, device=device, dtype=dtype, **kw)
+
+    # ------------------------------------------------------------------ op wrappers
+    def _new(self, *shape, dtype=None):
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def _linear(self, a: torch.Tensor, w: torch.Tensor, epi: int = cabi.EPI_NONE, out_f32: bool = False) -> torch.Tensor:
+        """out = a w^T (+ the gated pairing of stacked [Wg; Wu] weights), rounded to the model dtype."""
+        M, K = a.shape
+        N = w.shape[0] // 2 if epi in (cabi.EPI_GEGLU, cabi.EPI_SWIGLU) else w.shape[0]
+        out = self._new(M, N, dtype=torch.float32 if out_f32 else None)
+        L, st = cabi.lib(), cabi.stream()
+        if self.small_m_gemv and M <= self.gemv_max_rows and K % self.vec == 0 and a.is_contiguous():
+            # a handful of rows (decode steps): the weight-streaming GEMV kernel of the decode path; the gated pairing
+            # and the fp32 copy of the logits (rounded to the model dtype first, as the GEMM epilogue does) follow
+            if epi == cabi.EPI_NONE:
+                tmp = self._new(M, N) if out_f32 else out
+                cabi.check(L.pg_gemv_res(ptr(tmp), ptr(a), ptr(w), None, M, N, K, None, self.dt, st), "gemv")
+                if out_f32:
+                    out.copy_(tmp)
+                return out
+            if epi in (cabi.EPI_SWIGLU, cabi.EPI_GEGLU) and not out_f32:
+                gu = self._new(M, 2 * N)
+                cabi.check(L.pg_gemv_res(ptr(gu), ptr(a), ptr(w), None, M, 2 * N, K, None, self.dt, st), "gemv")
+                pair = L.pg_swiglu if epi == cabi.EPI_SWIGLU else L.pg_geglu
+                cabi.check(pair(ptr(out), ptr(gu), M, N, self.dt, st), "gated pairing")
+                return out
+        cabi.check(L.pg_gemm(ptr(out), ptr(a), ptr(w), None, None, M, N, K, a.stride(0), w.stride(0), out.stride(0), 0, 0,
+                             epi, 1 if out_f32 else 0, self.gemm_impl, self.dt, st), "gemm")
+        return out
+
+    # ------------------------------------------------------------------ one step
+    @staticmethod
+    def _segments(slots: Sequence[int], positions: Sequence[int]) -> List[int]:
+        """{slot, first row, tokens} of every run of one sequence's tokens; a sequence has ONE run per step."""
+        segs: List[int] = []
+        seen = set()
+        t0, T = 0, len(slots)
+        while t0 < T:
+            t1 = t0 + 1
+            while t1 < T and slots[t1] == slots[t0]:
+                if positions[t1] != positions[t1 - 1] + 1:
+                    raise ValueError("the tokens of a sequence must sit at consecutive positions within a step")
+                t1 += 1
+            if slots[t0] in seen:
+                raise ValueError("the tokens of a sequence must be consecutive rows of a step")
+            seen.add(slots[t0])
+            segs += [int(slots[t0]), t0, t1 - t0]
+            t0 = t1
+        return segs
+
+    @torch.no_grad()
+    def forward_tokens(self, kv, ids: Sequence[int], slots: Sequence[int], positions: Sequence[int],
+                       want_rows: Sequence[int], layer_sink: Optional[list] = None) -> torch.Tensor:
+        """Run the listed tokens (token t: id, page-table row of its sequence, position in it) through the model
+        from the cache and state that earlier steps left, append their keys and values, and return the fp32 logits
+        [len(want_rows), vocab] of the listed rows.  `kv` is the scheduler's slot table; its pages for the new
+        positions must be reserved (SlotKV.ensure).  layer_sink (debugging): receives the residual stream after
+        every layer."""
+        T, nw = len(ids), len(want_rows)
+        if T == 0:
+            return torch.empty((0, self.cfg.vocab), dtype=torch.float32, device=self.device)
+        if self.max_positions is not None and max(positions) >= self.max_positions:
+            raise ValueError(f"position {max(positions)} exceeds max_positions {self.max_positions}")
+        segs: List[int] = []
+        if self.needs_segments:
+            segs = self._segments(slots, positions)
+            n_max = min(T, int(kv.page_table.shape[0]))
+            segs += [0, 0, 0] * (n_max - len(segs) // 3)
+        ns = len(segs) // 3
+        # query tiles of the tensor-core attention: runs of <= 128 consecutive tokens of one sequence
+        tiles: List[int] = []
+        if T >= self.attn_tc_min_tokens and self._attn_tc_any:
+            t0 = 0
+            while t0 < T:
+                t1 = t0 + 1
+                while t1 < T and t1 - t0 < 128 and slots[t1] == slots[t0] and positions[t1] == positions[t1 - 1] + 1:
+                    t1 += 1
+                tiles += [t0, t1 - t0, int(slots[t0]), int(positions[t0])]
+                t0 = t1
+        nt = len(tiles) // 4
+        host = torch.empty(4 * T + nw + 3 * ns + 4 * nt, dtype=torch.int32).pin_memory()
+        host[:2 * T].view(torch.int64).copy_(torch.as_tensor(ids, dtype=torch.int64))
+        host[2 * T:3 * T].copy_(torch.as_tensor(slots, dtype=torch.int32))
+        host[3 * T:4 * T].copy_(torch.as_tensor(positions, dtype=torch.int32))
+        if nw:
+            host[4 * T:4 * T + nw].copy_(torch.as_tensor(want_rows, dtype=torch.int32))
+        if ns:
+            host[4 * T + nw:4 * T + nw + 3 * ns].copy_(torch.as_tensor(segs, dtype=torch.int32))
+        if nt:
+            host[4 * T + nw + 3 * ns:].copy_(torch.as_tensor(tiles, dtype=torch.int32))
+        if (T <= self.graph_max_tokens and layer_sink is None and not self._op_timing and nt == 0
+                and not torch.cuda.is_current_stream_capturing()):
+            return self._replay(kv, host, T, nw, ns)
+        return self._forward_device(kv, self._inputs(host.to(self.device, non_blocking=True), T, nw, ns), layer_sink)
+
+    @staticmethod
+    def _inputs(dev: torch.Tensor, T: int, nw: int, ns: int) -> StepInputs:
+        a = 4 * T + nw
+        return StepInputs(T=T, nw=nw, ids=dev[:2 * T].view(torch.int64), slot=dev[2 * T:3 * T], pos=dev[3 * T:4 * T],
+                          want=dev[4 * T:a], segs=dev[a:a + 3 * ns], n_segs=ns, tiles=dev[a + 3 * ns:],
+                          n_tiles=(dev.numel() - a - 3 * ns) // 4)
+
+    def _replay(self, kv, host: torch.Tensor, T: int, nw: int, ns: int) -> torch.Tensor:
+        """Small steps are launch-bound (some fifteen launches per layer): the kernel sequence for (T tokens, nw
+        wanted rows) over this slot table is captured once; a step copies its ids / slots / positions into the
+        graph's static input and replays.  Which kernels run depends on the counts only, never on the values."""
+        key = (T, nw, ns, kv.page_table.data_ptr(), kv.max_pages)
+        ent = self._graphs.get(key)
+        if ent is None:
+            static_in = torch.zeros(host.numel(), dtype=torch.int32, device=self.device)
+            static_in.copy_(host, non_blocking=True)
+            # warm-up outside the capture (module loading, shared-memory attributes) on inputs that touch no sequence:
+            # empty segments leave every recurrent state alone, and the cache rows it writes are rewritten by the replay
+            warm = static_in.clone()
+            if ns:
+                warm[4 * T + nw:].zero_()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._forward_device(kv, self._inputs(warm, T, nw, ns), None)
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self._forward_device(kv, self._inputs(static_in, T, nw, ns), None)
+            ent = self._graphs[key] = (g, static_in, out)
+            if len(self._graphs) > 64:
+                self._graphs.pop(next(iter(self._graphs)))
+        g, static_in, out = ent
+        static_in.copy_(host, non_blocking=True)
+        g.replay()
+        return out.clone()
+
+    def _forward_device(self, kv, inp: StepInputs, layer_sink: Optional[list]) -> torch.Tensor:
+        raise NotImplementedError
+
+    # ------------------------------------------------------------------ per-op timing (diagnostic: PG_OP_TIMING=1)
+    def _tm(self, name):
+        """CUDA-event bracket around one op when op timing is on (durations inside the real step, with the L2 state
+        of the real step); `op_times()` sums them per name.  A no-op otherwise."""
+        from .engine import PaliGemmaEngine
+        if not self._op_timing:
+            return PaliGemmaEngine._NoTimer()
+        return PaliGemmaEngine._EvTimer(self._op_events, name)
+
+    def op_times(self, reset: bool = True) -> Dict[str, float]:
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        for name, e0, e1 in self._op_events:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        if reset:
+            self._op_events = []
+        return out
+
+    # ------------------------------------------------------------------ serving glue
+    def new_batcher(self, **kw):
+        from .scheduler import RaggedBatcher
+        return RaggedBatcher(self, **kw)
+
+    def new_slot_state(self, slots: int):
+        """Recurrent state of `slots` sequences (scheduler.SlotState), None for designs without any."""
+        return None
+
+    _ERR_TEXT = {2: "a tensor-core kernel gave up waiting on its pipeline (its results are invalid)"}
+
+    def check_errors(self, sync: bool = False) -> None:
+        if sync:
+            torch.cuda.current_stream(self.device).synchronize()
+        if self._err_np[0] != 0:
+            code, self._err_np[0] = int(self._err_np[0]), 0
+            raise RuntimeError(self._ERR_TEXT.get(code, "a token id lies outside the vocabulary or a position outside "
+                                                        "the positions the model has"))

@@ -40,6 +40,7 @@ class SlotKV(PagedKV):
         self.page_table = torch.full((slots, self.max_pages), self.parking, dtype=torch.int32, device=engine.device)
         self.host_len = [0] * slots          # KV entries per slot (host mirror; 0 = idle)
         self.active = [False] * slots
+        self.state: Optional["SlotState"] = None   # recurrent state per slot, for engines whose design has any
 
     def reserve(self, total_len: int) -> None:   # DecodeState.run_steps calls this with the uniform-length view
         return
@@ -53,6 +54,8 @@ class SlotKV(PagedKV):
         self.kv_len[slot:slot + 1].fill_(length)
         self.host_len[slot] = length
         self.active[slot] = True
+        if self.state is not None and length == 0:
+            self.state.reset(slot)           # a new sequence starts from the zero state, whoever held the slot before
 
     def ensure(self, slot: int, total_len: int) -> None:
         """Pages for `total_len` entries of the sequence in `slot` (called before the steps that need them)."""
@@ -79,6 +82,24 @@ class SlotKV(PagedKV):
             self.engine._free_pages([self.parking])
             self.parking = None
         super().release()
+
+
+class SlotState:
+    """Recurrent state of the sequences in the scheduler's slots: one fp32 tensor [slots, ...] per recurrent layer,
+    addressed by the same slot index as the page table's rows.  A slot's rows are zeroed when a new sequence takes
+    it; between steps the state simply stays where the step's kernels left it."""
+
+    def __init__(self, slots: int, shapes: Dict[int, tuple], device):
+        self.slots = int(slots)
+        self.layers: Dict[int, torch.Tensor] = {
+            i: torch.zeros((self.slots,) + tuple(shape), dtype=torch.float32, device=device) for i, shape in shapes.items()}
+
+    def reset(self, slot: int) -> None:
+        for t in self.layers.values():
+            t[slot].zero_()
+
+    def bytes(self) -> int:
+        return sum(t.numel() * 4 for t in self.layers.values())
 
 
 @dataclass
@@ -270,8 +291,14 @@ class RaggedBatcher:
         self.slots = int(slots)
         ps = engine.page_size
         pool_tokens = (engine.num_pages - 1) * ps
-        cap = min(pool_tokens, engine.cfg.max_positions if max_seq_tokens is None else int(max_seq_tokens))
+        limit = getattr(engine, "max_positions", getattr(getattr(engine, "cfg", None), "max_positions", None))
+        # None: the design addresses any position
+        cap = pool_tokens if limit is None else min(pool_tokens, limit)
+        if max_seq_tokens is not None:
+            cap = min(pool_tokens, int(max_seq_tokens))
+        self.max_seq = cap if limit is None else min(cap, limit)
         self.kv = SlotKV(engine, self.slots, max(cap, ps))
+        self.kv.state = engine.new_slot_state(self.slots) if hasattr(engine, "new_slot_state") else None
         self.token_budget = max(1, int(token_budget))
         self.sample = (float(temperature), float(top_p), int(seed)) if do_sample else None
         self.slot_of: Dict[object, int] = {}          # sequence key -> slot
@@ -326,10 +353,10 @@ class RaggedBatcher:
         prompt = [int(t) for t in (prompt.flatten().tolist() if isinstance(prompt, torch.Tensor) else prompt)]
         if not prompt or max_new_tokens < 1:
             raise ValueError("a request needs a prompt and max_new_tokens >= 1")
-        cap = self.kv.max_pages * self.eng.page_size
-        if len(prompt) + int(max_new_tokens) > min(cap, self.eng.cfg.max_positions):
+        cap = min(self.kv.max_pages * self.eng.page_size, self.max_seq)
+        if len(prompt) + int(max_new_tokens) > cap:
             raise ValueError(f"prompt ({len(prompt)}) + max_new_tokens ({max_new_tokens}) exceeds the capacity of "
-                             f"{min(cap, self.eng.cfg.max_positions)} tokens per sequence")
+                             f"{cap} tokens per sequence")
         r = TokenRequest(prompt, int(max_new_tokens), eos_token_id, self._next_rid)
         self._next_rid += 1
         self.queue.append(r)
