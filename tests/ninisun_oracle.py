@@ -62,19 +62,26 @@ def rotate_pairs(x, cos, sin):
     return x
 
 
+def visible(T, size, keep_first):
+    """[T, T] matrix: key j is visible to query i when j <= i and (i - j < size or j < keep_first); size <= 0: all j <= i."""
+    vis = torch.zeros(T, T, dtype=torch.bool)
+    for i in range(T):
+        for j in range(i + 1):
+            vis[i, j] = size <= 0 or i - j < size or j < keep_first
+    return vis
+
+
 def window_softmax_attention(q, k, v, scale, size, keep_first):
-    """q [T, H, d], k [T, G, d], v [T, G, e] of ONE sequence from position 0.  Key j is visible to query i when
-    j <= i and (i - j < size or j < keep_first); size <= 0: every j <= i."""
+    """q [T, H, d], k [T, G, d], v [T, G, e] of ONE sequence from position 0; softmax over the visible keys."""
     T, H, _ = q.shape
     G = k.shape[1]
+    vis = visible(T, size, keep_first)
     out = torch.zeros(T, H, v.shape[2], dtype=F64)
-    for i in range(T):
-        js = [j for j in range(i + 1) if size <= 0 or i - j < size or j < keep_first]
-        for n in range(H):
-            g = n // (H // G)
-            s = torch.stack([(q[i, n] * k[j, g]).sum() * scale for j in js])
-            p = torch.softmax(s, 0)
-            out[i, n] = (p[:, None] * v[js, g]).sum(0)
+    for n in range(H):
+        g = n // (H // G)
+        s = (q[:, n] @ k[:, g].T) * scale
+        p = torch.softmax(s.masked_fill(~vis, -math.inf), -1)
+        out[:, n] = p @ v[:, g]
     return out
 
 
@@ -195,3 +202,85 @@ def forward(cfg, Wt, tokens, layer_sink=None):
         if layer_sink is not None:
             layer_sink.append(x.clone())
     return lin(Wt["embed"], rms_norm(x, Wt["final.norm"], eps))
+
+
+# ------------------------------------------------------------------ random checkpoints
+def make_config(vocab=96, width=48, eps=1e-5, layers=None):
+    return {"architecture": "Ninisun", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+
+
+def rot(dims, base=10000.0, scaling=None):
+    r = {"dims": dims, "base": base}
+    if scaling:
+        r["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return r
+
+
+def attn(heads=4, kv_heads=2, dim=8, vdim=16, scale=0.3, rot_dims=4, base=10000.0, window=24, keep_first=2, v_mix=True):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot_dims:
+        m["rot"] = rot(rot_dims, base)
+    if window:
+        m["mask"] = {"size": window, "keep_first": keep_first}
+    if v_mix:
+        m["v_mix"] = True
+    return m
+
+
+def parallel(heads=4, kv_heads=2, dim=8, vdim=16, scale=0.25, rot_dims=8, base=5000.0, scaling=(4.0, 64, 16.0, 1.0),
+             r_heads=3, r_dim=8, left_scale=0.7, right_scale=1.3):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot_dims:
+        left["rot"] = rot(rot_dims, base, scaling)
+    return {"left": left, "right": {"heads": r_heads, "dim": r_dim}, "left_scale": left_scale, "right_scale": right_scale}
+
+
+def layer(mixer, ff=40):
+    return {"type": "parallel" if "left" in mixer else "attention", "mixer": mixer,
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def make_checkpoint(cfg, seed=0, dtype=torch.bfloat16, lora=6):
+    """Random tensors under the checkpoint's names, rounded to `dtype` (engine and oracle then see the same numbers)."""
+    g = torch.Generator().manual_seed(seed)
+    D = cfg["width"]
+    T = {}
+
+    def lin(name, out, inp, gain=1.0):
+        T[name] = (torch.randn(out, inp, generator=g) * gain / math.sqrt(inp)).to(dtype)
+
+    def vec(name, n, mean=1.0, std=0.1):
+        T[name] = (mean + std * torch.randn(n, generator=g)).to(dtype)
+
+    T["embed"] = torch.randn(cfg["vocab"], D, generator=g).to(dtype)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for n in ("norm1", "norm1b"):
+            vec(p + n, D)
+        vec(p + "ls1", D, 0.5, 0.2)
+        if L["type"] == "attention":
+            H, G, d, e = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
+            lin(p + "mix.q", H * d, D, 2.0), lin(p + "mix.k", G * d, D, 2.0), lin(p + "mix.v", G * e, D), lin(p + "mix.o", D, H * e)
+            if m.get("v_mix"):
+                T[p + "mix.vmix"] = (0.2 + 0.6 * torch.rand((), generator=g)).to(dtype)
+        else:
+            l, r = m["left"], m["right"]
+            H, G, d, e = l["heads"], l.get("kv_heads", l["heads"]), l["dim"], l.get("vdim", l["dim"])
+            q = p + "mix.left."
+            lin(q + "q", H * d, D, 2.0), lin(q + "k", G * d, D, 2.0), lin(q + "v", G * e, D), lin(q + "o", D, H * e, 0.3)
+            vec(q + "q.b", H * d, 0.0, 0.3), vec(q + "k.b", G * d, 0.0, 0.3), vec(q + "v.b", G * e, 0.0, 0.3)
+            vec(q + "pb", H, -1.0, 1.0), lin(q + "g", H, D, 2.0)
+            nd, q = r["heads"] * r["dim"], p + "mix.right."
+            for n in ("r", "k", "v"):
+                lin(q + n, nd, D)
+            lin(q + "g", nd, D, 2.0), lin(q + "a", nd, D, 2.0), vec(q + "a.b", nd, 0.0, 0.5)
+            lin(q + "w1", lora, D, 2.0), lin(q + "w2", nd, lora, 2.0), vec(q + "w0", nd, 0.0, 1.0)
+            vec(q + "norm", nd), lin(q + "o", D, nd)
+        if L.get("mlp"):
+            ff = L["mlp"]["ff"]
+            for n in ("norm2", "norm2b"):
+                vec(p + n, D)
+            vec(p + "ls2", D, 0.5, 0.2)
+            lin(p + "mlp.gate", ff, D), lin(p + "mlp.up", ff, D), lin(p + "mlp.down", D, ff)
+    vec("final.norm", D)
+    return T
