@@ -311,6 +311,15 @@ int pg_attention_ragged_ex(void* out, int ld_out, const void* q, int ld_q, const
                            int keep_first, const float* slopes, int sigmoid_weights, const float* head_bias,
                            float out_scale, float* ws, long long ws_floats, int dtype, void* stream);
 
+/* pg_attention_ragged_tc with the extensions of pg_attention_ragged_ex (kept first positions, sigmoid weights with a
+ * per-head bias in ONE pass over the key tiles, per-head gate, out_scale). */
+int pg_attention_ragged_tc_ex(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                              int gate_per_head, const void* k_pool, const void* v_pool, long long pool_rows,
+                              const int32_t* page_table, int pt_stride, int page_size, const int32_t* tiles,
+                              int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim, float scale,
+                              int window, int keep_first, const float* slopes, int sigmoid_weights,
+                              const float* head_bias, float out_scale, int* err_flag, int dtype, void* stream);
+
 /* Bias, rotary positions, value mixing and cache append for one fused projection row per token: proj row holds
  * n_heads query heads and n_kv_heads key heads of `dim` columns and n_kv_heads value heads of `vdim` columns at the
  * given offsets.  Biases (model dtype, may be NULL) are added first.  The first rot_dims columns of every query and

@@ -10,6 +10,10 @@
 //   pass 1: S again (K double-buffered, V in one buffer), p = exp(s - max) in fp32, row sum from the fp32 values, P rounded to the model dtype into a
 //           K-major SWIZZLE_128B tile, O += P V with V as an MN-major operand straight from its [key, vdim] page.
 // Epilogue: O / sum, times sigmoid(gate), rounded once.  Key width and value width are independent multiples of 64.
+// Extensions (pg_attention_ragged_tc_ex): keep_first > 0 keeps the first keep_first positions visible behind the
+// window: the key tiles are then the pages that hold them (as far as they lie before the window's first page)
+// followed by the window's pages.  sigmoid_weights: ONE pass, p = sigmoid(s + head_bias[h]), no maximum, no sum.  The
+// gate may be one value per (token, head); the result is multiplied by out_scale before it is rounded.
 // Every mbarrier wait is bounded: a wait that gives up sets the error flag, the roles leave their loops, the CTA lets
 // its copies land, frees its TMEM and returns.
 #include <cmath>
@@ -48,6 +52,10 @@ struct WinParams {
   float scale; int window;
   const float* slopes;
   int* err_flag;
+  int keep_first, sigmoid_weights;
+  const float* head_bias;
+  int gate_per_head;
+  float out_scale;
 };
 
 template <typename T>
@@ -99,8 +107,13 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int row0 = tile[0], rows = tile[1], slot = tile[2], pos0 = tile[3];
   const int hi = pos0 + rows - 1;                                        // last key position any row can see
   const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;         // first one
-  const int t_lo = lo / WK, n_tiles = hi / WK - t_lo + 1;
+  const int t_lo = lo / WK;
+  // pages of the kept first positions that lie before the window's first page, then the window's pages
+  const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + WK - 1) / WK, t_lo) : 0;
+  const int n_tiles = n_keep + hi / WK - t_lo + 1;
+  auto page_of = [&](int t) { return t < n_keep ? t : t_lo + (t - n_keep); };   // key tile -> page of the sequence
   const int32_t* pt_row = p.page_table + (size_t)slot * p.pt_stride;
+  const bool sig = p.sigmoid_weights != 0;
 
   if (warp == 0 && lane == 0) {
     // ===================== TMA + MMA issuer (one thread) =====================
@@ -109,16 +122,16 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     mbar_expect_tx(bar_q, Q_BYTES);
     for (int kb = 0; kb < KB; ++kb)
       tma_load_2d(s_q + kb * (WQ * 128), &map_q, bar_q, h * p.dim + kb * 64, row0);
-    const int total = 2 * n_tiles;
+    const int total = sig ? n_tiles : 2 * n_tiles;
     auto request = [&](int i) {   // K of flat step i into K buffer i & 1
-      const int pass = i >= n_tiles ? 1 : 0, t = t_lo + (pass ? i - n_tiles : i), bf = i & 1;
+      const int t = page_of(i >= n_tiles ? i - n_tiles : i), bf = i & 1;
       const int row = pt_row[t] * WK;
       mbar_expect_tx(bar_kv(bf), K_BYTES);
       for (int kb = 0; kb < KB; ++kb)
         tma_load_2d(s_k(bf) + kb * (WK * 128), &map_k, bar_kv(bf), kvh * p.dim + kb * 64, row);
     };
     auto request_v = [&](int t) {   // V of key tile t (pass 1) into the V buffer
-      const int row = pt_row[t_lo + t] * WK;
+      const int row = pt_row[page_of(t)] * WK;
       mbar_expect_tx(bar_v, V_BYTES);
       for (int vb = 0; vb < VB; ++vb)
         tma_load_2d(s_vb + vb * (WK * 128), &map_v, bar_v, kvh * p.vdim + vb * 64, row);
@@ -126,7 +139,7 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     request(0);
     if (!wait_lim(bar_q, 0, fail)) goto issuer_done;
     for (int it = 0; it < total; ++it) {
-      const int pass = it >= n_tiles ? 1 : 0, t = pass ? it - n_tiles : it, bf = it & 1;
+      const int pass = (sig || it >= n_tiles) ? 1 : 0, t = it >= n_tiles ? it - n_tiles : it, bf = it & 1;
       if (it > 0 && !wait_lim(bar_sfree, (it - 1) & 1, fail)) goto issuer_done;          // S of the previous tile was read
       if (pass == 1 && t > 0 && !wait_lim(bar_o, (t - 1) & 1, fail)) goto issuer_done;   // previous PV done with V and P
       if (pass == 1) request_v(t);                                 // lands behind S(it) and the softmax of this tile
@@ -155,16 +168,16 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const int qw = warp & 3, r = qw * 32 + lane;
     const uint32_t t_row = tmem_base + ((uint32_t)(qw * 32) << 16);
     const int i = pos0 + r;                                        // this row's position
-    const float slope = p.slopes ? p.slopes[h] : 0.f;
+    const float slope = p.slopes ? p.slopes[h] : 0.f, hbias = p.head_bias ? p.head_bias[h] : 0.f;
     float m = -INFINITY, l = 0.f;
     int it = 0;
     bool ok = true;
-    for (int pass = 0; pass < 2 && ok; ++pass) {
+    for (int pass = sig ? 1 : 0; pass < 2 && ok; ++pass) {
       for (int t = 0; t < n_tiles; ++t, ++it) {
         if (!wait_lim(bar_s, it & 1, fail)) { ok = false; break; }
         tc_fence_after();
         if (pass == 1 && t > 0 && !wait_lim(bar_o, (t - 1) & 1, fail)) { ok = false; break; }   // P buffer is free again
-        const int j0 = (t_lo + t) * WK;
+        const int j0 = page_of(t) * WK;
 #pragma unroll 1
         for (int c = 0; c < WK / 32; ++c) {
           float s[32];
@@ -172,16 +185,19 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           tmem_ld_wait();
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) {
-            const int back = i - (j0 + c * 32 + jj);               // i - j
-            const bool vis = back >= 0 && (p.window <= 0 || back < p.window);
-            s[jj] = vis ? s[jj] * p.scale - slope * (float)back : -INFINITY;
+            const int j = j0 + c * 32 + jj, back = i - j;
+            const bool vis = back >= 0 && (p.window <= 0 || back < p.window || j < p.keep_first);
+            s[jj] = vis ? s[jj] * p.scale - slope * (float)back + hbias : -INFINITY;
           }
           if (pass == 0) {
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj) m = fmaxf(m, s[jj]);
           } else {
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj) { s[jj] = __expf(s[jj] - m); l += s[jj]; }
+            for (int jj = 0; jj < 32; ++jj) {
+              s[jj] = sig ? 1.f / (1.f + __expf(-s[jj])) : __expf(s[jj] - m);   // exp(+inf) -> weight 0 when masked
+              l += s[jj];
+            }
             // P[r][c*32 .. +31] into the K-major SWIZZLE_128B tile (128 rows x 128 B)
             uint8_t* blk = p_ptr + r * 128;
 #pragma unroll
@@ -201,10 +217,12 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     }
     if (ok && wait_lim(bar_o, (n_tiles - 1) & 1, fail)) {
       tc_fence_after();
-      const float inv = 1.f / l;
+      float inv = (sig ? 1.f : 1.f / l) * p.out_scale;
       const size_t trow = (size_t)row0 + r;
       T* orow = reinterpret_cast<T*>(p.out) + trow * p.ld_out + (size_t)h * p.vdim;
-      const T* grow = p.gate ? reinterpret_cast<const T*>(p.gate) + trow * p.ld_gate + (size_t)h * p.vdim : nullptr;
+      const T* grow = (p.gate && !p.gate_per_head) ? reinterpret_cast<const T*>(p.gate) + trow * p.ld_gate + (size_t)h * p.vdim : nullptr;
+      if (p.gate && p.gate_per_head && r < rows)
+        inv *= 1.f / (1.f + __expf(-to_f<T>(reinterpret_cast<const T*>(p.gate)[trow * p.ld_gate + h])));
 #pragma unroll 1
       for (int c = 0; c * 32 < p.vdim; ++c) {
         float o[32];
@@ -252,17 +270,18 @@ extern "C" int pg_attention_ragged_tc_ok(int dim, int vdim, int page_size, int l
   return tc::encode_fn() != nullptr ? 1 : 0;
 }
 
-extern "C" int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
-                                      const void* k_pool, const void* v_pool, long long pool_rows,
-                                      const int32_t* page_table, int pt_stride, int page_size, const int32_t* tiles,
-                                      int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
-                                      float scale, int window, const float* slopes, int* err_flag, int dtype,
-                                      void* stream) {
+extern "C" int pg_attention_ragged_tc_ex(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                         int gate_per_head, const void* k_pool, const void* v_pool, long long pool_rows,
+                                         const int32_t* page_table, int pt_stride, int page_size, const int32_t* tiles,
+                                         int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
+                                         float scale, int window, int keep_first, const float* slopes,
+                                         int sigmoid_weights, const float* head_bias, float out_scale, int* err_flag,
+                                         int dtype, void* stream) {
   if (n_tiles <= 0) return PG_OK;
-  PG_REQUIRE(pg_attention_ragged_tc_ok(dim, vdim, page_size, ld_q, ld_out, ld_gate, dtype),
+  PG_REQUIRE(pg_attention_ragged_tc_ok(dim, vdim, page_size, ld_q, ld_out, (gate && !gate_per_head) ? ld_gate : 8, dtype),
              "attention_ragged_tc: unsupported problem (dim %d vdim %d page %d dtype %d)", dim, vdim, page_size, dtype);
   PG_REQUIRE(n_heads % n_kv_heads == 0, "attention_ragged_tc: heads %d / kv heads %d", n_heads, n_kv_heads);
-  PG_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)gate % 16) == 0 &&
+  PG_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)out % 16) == 0 && (gate_per_head || ((uintptr_t)gate % 16) == 0) &&
                  ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0,
              "attention_ragged_tc: operands must be 16-byte aligned");
   const bool bf = dtype == PG_BF16;
@@ -272,7 +291,8 @@ extern "C" int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int 
                  tc::make_map_2d(&mv, v_pool, pool_rows, (long long)n_kv_heads * vdim, (long long)n_kv_heads * vdim, tc::WK, bf),
              "attention_ragged_tc: cuTensorMapEncodeTiled failed");
   tc::WinParams p = {out, ld_out, gate, ld_gate, tiles, page_table, pt_stride, n_heads, n_heads / n_kv_heads, dim, vdim,
-                     scale, window, slopes, err_flag};
+                     scale, window, slopes, err_flag, keep_first, sigmoid_weights ? 1 : 0, head_bias,
+                     gate_per_head ? 1 : 0, out_scale};
   const size_t smem = 1024 + (size_t)tc::WQ * dim * 2 + 2 * (size_t)tc::WK * dim * 2 + (size_t)tc::WK * vdim * 2 +
                       (size_t)tc::WQ * tc::WK * 2 + 72 + 16;
   cudaStream_t st = (cudaStream_t)stream;
@@ -287,4 +307,15 @@ extern "C" int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int 
   PG_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
              "attention_ragged_tc: cannot reserve %zu B of shared memory", smem);
   return launch_tc("attention_ragged_tc", kern, grid, dim3(256), smem, 1, false, st, mq, mk, mv, p);
+}
+
+extern "C" int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                      const void* k_pool, const void* v_pool, long long pool_rows,
+                                      const int32_t* page_table, int pt_stride, int page_size, const int32_t* tiles,
+                                      int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
+                                      float scale, int window, const float* slopes, int* err_flag, int dtype,
+                                      void* stream) {
+  return pg_attention_ragged_tc_ex(out, ld_out, q, ld_q, gate, ld_gate, 0, k_pool, v_pool, pool_rows, page_table, pt_stride,
+                                   page_size, tiles, n_tiles, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, 0,
+                                   slopes, 0, nullptr, 1.f, err_flag, dtype, stream);
 }

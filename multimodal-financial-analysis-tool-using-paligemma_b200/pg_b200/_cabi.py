@@ -76,6 +76,8 @@ SIGNATURES = {
     "pg_geglu": [_vp, _vp, _i, _i, _i, _vp],
     "pg_attention_ragged_ex": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
                                _i, _vp, _i, _vp, _f, _vp, _ll, _i, _vp],
+    "pg_attention_ragged_tc_ex": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _f,
+                                  _i, _i, _vp, _i, _vp, _f, _vp, _i, _vp],
     "pg_rotary_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _i, _vp, _i, _f, _vp, _vp,
                          _vp, _i, _i, _vp, _vp, _i, _i, _vp],
     "pg_postnorm_residual": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _i, _vp],

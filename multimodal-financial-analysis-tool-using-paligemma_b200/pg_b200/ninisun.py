@@ -179,7 +179,7 @@ class NinisunEngine(RaggedEngine):
         L_ = cabi.lib()
         for w, lc in zip(self.layers, self.cfg.layers):
             a = lc.attn
-            w["attn_tc"] = bool(getattr(L_, "pg_attention_ragged_tc_ex", None)) and bool(L_.pg_attention_ragged_tc_ok(
+            w["attn_tc"] = bool(L_.pg_attention_ragged_tc_ok(
                 a.dim, a.vdim, self.page_size, a.heads * a.dim, w["att_cols"], w["proj"].shape[0], self.dt))
         self._attn_tc_any = any(w["attn_tc"] for w in self.layers)
         self._init_runtime(kv_pool_tokens)

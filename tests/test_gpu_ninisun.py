@@ -160,8 +160,9 @@ def test_rotary_append_bias_value_mixing(dim, rot_dims, scaling, biased, mix):
     assert bool((pg.k.view(-1, nk).cpu()[untouched] == 7.0).all())
 
 
-def _attention_case(H, G, dim, vdim, window, keep, lens, new, sigmoid, dtype=torch.float32, tower=None, seed=0):
-    """Sequences of lens[s] cached tokens of which the last new[s] are this step's queries; returns (got, want)."""
+def _attention_case(H, G, dim, vdim, window, keep, lens, new, sigmoid, dtype=torch.float32, tower=None, seed=0, tc=False):
+    """Sequences of lens[s] cached tokens of which the last new[s] are this step's queries; returns (got, want).
+    tc: through the tensor-core kernel (query tiles of up to 128 consecutive tokens of one sequence)."""
     cabi, L, st = _lib()
     g = torch.Generator().manual_seed(seed)
     pg = Paged(lens, G * dim, G * vdim, dtype)
@@ -198,6 +199,23 @@ def _attention_case(H, G, dim, vdim, window, keep, lens, new, sigmoid, dtype=tor
     gate = torch.cat(gate_rows).to(dtype).cuda() if sigmoid else None
     pbd = pb.cuda()
     ws = torch.empty(1 << 20, device="cuda")
+    if tc:
+        tiles, t0 = [], 0
+        while t0 < T:
+            t1 = t0 + 1
+            while t1 < T and t1 - t0 < 128 and slots[t1] == slots[t0]:
+                t1 += 1
+            tiles += [t0, t1 - t0, slots[t0], positions[t0]]
+            t0 = t1
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        cabi.check(L.pg_attention_ragged_tc_ex(
+            out.data_ptr(), H * vdim + 8, q_all.data_ptr(), H * dim, None if gate is None else gate.data_ptr(), H,
+            1 if sigmoid else 0, pg.k.data_ptr(), pg.v.data_ptr(), pg.k.shape[0] * PAGE, pg.table.data_ptr(), pg.max_pages,
+            PAGE, _i32(tiles).data_ptr(), len(tiles) // 4, T, H, G, dim, vdim, scale, window, keep, None,
+            1 if sigmoid else 0, pbd.data_ptr() if sigmoid else None, 0.8 if sigmoid else 1.0, err.data_ptr(), CT[dtype], st))
+        torch.cuda.synchronize()
+        assert int(err) == 0
+        return out[:, :H * vdim].float(), torch.cat(want)
     cabi.check(L.pg_attention_ragged_ex(
         out.data_ptr(), H * vdim + 8, q_all.data_ptr(), H * dim, None if gate is None else gate.data_ptr(), H,
         1 if sigmoid else 0, pg.k.data_ptr(), pg.v.data_ptr(), pg.table.data_ptr(), pg.max_pages, PAGE,
@@ -236,6 +254,30 @@ def test_sigmoid_attention_head_bias_head_gate(H, G, dim, vdim):
     _rows_close(got, want, 2e-5)
     got, want = _attention_case(H, G, dim, vdim, 0, 0, lens=[700], new=[1], sigmoid=True, tower=lambda i: 3)
     _rows_close(got, want, 2e-5)
+
+
+@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 64, 128), (2, 1, 128, 64), (2, 2, 64, 64)])
+@pytest.mark.parametrize("window,keep", [(0, 0), (100, 3), (70, 66), (64, 130), (200, 0), (5, 1)])
+@pytest.mark.parametrize("sigmoid", [False, True])
+def test_tensor_core_attention_portions_windows_kept_tokens(H, G, dim, vdim, window, keep, sigmoid):
+    """16-bit prompt portions on the tcgen05 kernel: a portion that starts in the middle of a page and a window, a
+    two-token portion and single tokens in one launch; softmax weights are rounded to 16 bits as the operand of P V."""
+    if sigmoid and (window or keep):
+        pytest.skip("the sigmoid attention of this design is unmasked")
+    got, want = _attention_case(H, G, dim, vdim, window, keep, lens=[300, 1, 150, 66], new=[200, 1, 40, 2], sigmoid=sigmoid,
+                                dtype=torch.bfloat16, tc=True)
+    _rows_close(got, want, 2e-2)
+
+
+@pytest.mark.parametrize("window,keep", [(72, 4), (100, 64), (70, 0), (130, 65)])
+@pytest.mark.parametrize("where", ["window_in", "window_out", "first_in", "first_out"])
+def test_tensor_core_attention_towering_key_at_every_edge(window, keep, where):
+    tower = {"window_in": lambda i: i - window + 1, "window_out": lambda i: i - window,
+             "first_in": lambda i: keep - 1, "first_out": lambda i: keep}[where]
+    for n in (window + keep + 9, 257, 400):
+        got, want = _attention_case(4, 2, 64, 64, window, keep, lens=[n, 90], new=[min(150, n), 1], sigmoid=False,
+                                    dtype=torch.bfloat16, tower=tower, seed=n, tc=True)
+        _rows_close(got, want, 2e-2)
 
 
 @pytest.mark.parametrize("heads,dim,lora", [(3, 8, 6), (1, 48, 16), (2, 64, 5), (2, 100, 8), (1, 130, 4)])
