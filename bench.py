@@ -660,19 +660,21 @@ def run_ours(args, rank, world, local):
 
 
 def run_arch(args):
-    """`--arch mubasun`: see pg_b200/arch_bench.py.  One JSON line; `value` is the prefill throughput at the largest
-    size, the rest (decode, per-op rooflines, the Gemma decoder's numbers) rides along."""
+    """`--arch mubasun | ninisun`: see pg_b200/arch_bench.py.  One JSON line; `value` is the prefill throughput at the
+    largest size, the rest (decode, per-op rooflines, the numbers of the closest existing model at equal size) rides
+    along."""
     from pg_b200 import arch_bench
     torch.cuda.set_device(0)
     pk = measured_peaks()
     sizes = [x for x in args.arch_sizes.split(",") if x]
     with ClockSampler(0) as clk:
-        res = arch_bench.run(sizes, steps=min(args.steps, 16), warmup=args.warmup, peaks=pk)
+        runner = arch_bench.run_ninisun if args.arch == "ninisun" else arch_bench.run
+        res = runner(sizes, steps=min(args.steps, 16), warmup=args.warmup, peaks=pk)
     head = res[sizes[-1]]
-    emit({"metric": "mubasun_prefill_tokens_per_s", "value": head["prefill"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
+    emit({"metric": f"{args.arch}_prefill_tokens_per_s", "value": head["prefill"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
           "steps": min(args.steps, 16), "warmup": args.warmup, "ms_per_step": head["prefill"]["ms"],
           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-          "config": {"model": f"Mubasun {sizes[-1]} (random weights)", "global_batch": head["prefill"]["sequences"],
+          "config": {"model": f"{args.arch.capitalize()} {sizes[-1]} (random weights)", "global_batch": head["prefill"]["sequences"],
                      "seq_len": head["prefill"]["tokens"] // head["prefill"]["sequences"], "parallelism": "single GPU",
                      "l2": "256 MB scratch write between timed steps"},
           "peaks": pk, "clocks": clk.summary(), "gpu_launches": res.pop("gpu_launches"), "sizes": res})
@@ -713,9 +715,10 @@ def main():
                     help="N > 1: what `value` measures. tp = ONE sequence, tensor-parallel decoder (strong scaling, the north "
                          "star's sharding); replicas = one independent sequence per GPU (weak scaling, no data-path "
                          "collective).  Both are measured in every N > 1 run; the other one is reported beside the headline.")
-    ap.add_argument("--arch", default=None, choices=["mubasun"],
+    ap.add_argument("--arch", default=None, choices=["mubasun", "ninisun"],
                     help="instead of the default workload: prefill / decode throughput of this decoder-only design at "
-                         "real-model layer sizes (random weights) beside the Gemma decoder at equal size, one GPU")
+                         "real-model layer sizes (random weights) beside the closest existing model at equal size (the "
+                         "Gemma decoder for mubasun, a dense Mubasun for ninisun), one GPU")
     ap.add_argument("--arch-sizes", default="w1024,w2048")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

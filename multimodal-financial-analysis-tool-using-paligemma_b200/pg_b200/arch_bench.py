@@ -1,6 +1,8 @@
 """`bench.py --arch mubasun`: prefill and decode throughput of the Mubasun engine at layer sizes that resemble a
 real model's (random weights), beside the framework's Gemma decoder (the text half of the PaliGemma engine) at equal
 width, depth, query width and feed-forward size, with a per-kernel roofline table for both.
+`bench.py --arch ninisun`: the same for the Ninisun engine beside the closest model the framework serves the same
+way, a dense Mubasun of equal width, depth, head layout, window and feed-forward width (`run_ninisun`).
 
 Timing: CUDA events on the launching stream, >= 3 warm-up steps, an L2-sized scratch write between timed steps.
 Roofline of an op = max(algorithmic FLOPs / measured bf16 peak, algorithmic bytes / measured copy bandwidth);
@@ -218,6 +220,58 @@ LIKE = [("norm", "t_norm"), ("proj", "t_qkv"), ("qknorm_append", "t_rope_append"
         ("moe_down", "t_down"), ("shared_gate_up", "t_gate_up"), ("shared_down", "t_down")]
 
 
+def _measure_ragged(eng, vocab: int, timer, steps, warmup, peaks, work, decode_bytes, prefill_tokens, prefill_seqs, context,
+                    decode_batches) -> dict:
+    """Prefill (all prompts in ONE step), per-op rooflines of that step, and decode steps of an engine that is served
+    through RaggedBatcher.  work: name -> (FLOPs, bytes) of the prefill step; decode_bytes(B): weight bytes of a step."""
+    row = {}
+    slots = max(max(decode_batches), prefill_seqs)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, vocab, (prefill_tokens,), generator=g).tolist() for _ in range(prefill_seqs)]
+    b = eng.new_batcher(slots=slots + 1, max_seq_tokens=max(prefill_tokens, context) + 256)
+    T_all = prefill_tokens * prefill_seqs
+
+    def prefill():                                   # all prompts in ONE step of the engine
+        for i in range(prefill_seqs):
+            b.admit(("p", i))
+        b.run_entries([(("p", i), prompts[i], [prefill_tokens - 1]) for i in range(prefill_seqs)])
+
+    def drop():
+        for i in range(prefill_seqs):
+            if ("p", i) in b.slot_of:
+                b.finish(("p", i))
+    ms = timer.run(prefill, steps, warmup, setup=drop)
+    drop()
+    row["prefill"] = {"tokens": T_all, "sequences": prefill_seqs, "ms": round(_med(ms), 3),
+                      "tok_s": round(T_all / _med(ms) * 1e3), "min_ms": round(min(ms), 3), "max_ms": round(max(ms), 3)}
+    eng._op_timing = True                                    # one more prefill, bracketed op by op
+    for _ in range(2):
+        prefill(); drop(); eng.op_times()
+    reps = 3
+    for _ in range(reps):
+        timer.scratch.zero_(); prefill(); drop()
+    times = {k: v / reps for k, v in eng.op_times().items()}
+    eng._op_timing = False
+    row["prefill_ops"] = _roofline(work, times, peaks)
+    row["decode"] = {}
+    for B in decode_batches:
+        for i in range(B):
+            b.admit(("d", i))
+        ctx = torch.randint(0, vocab, (context,), generator=g).tolist()
+        for i in range(B):
+            b.run_entries([(("d", i), ctx, [])])
+        step_ents = [(("d", i), [7 + i], [0]) for i in range(B)]
+        n_dec = min(steps * 4, 200)
+        ms = timer.run(lambda: b.run_entries(step_ents), n_dec, warmup + 2)
+        row["decode"][f"batch{B}"] = {"context": context, "ms_per_step": round(_med(ms), 4),
+                                      "tok_s": round(B / _med(ms) * 1e3), "graph": eng.graph_max_tokens >= B,
+                                      "weight_stream_ms": round(decode_bytes(B) / (peaks["hbm"] * 1e9) * 1e3, 4)}
+        for i in range(B):
+            b.finish(("d", i))
+    b.close()
+    return row
+
+
 @torch.no_grad()
 def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, prefill_seqs=4, context=1024,
         decode_batches=(1, 8)) -> dict:
@@ -235,50 +289,12 @@ def run(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, prefil
         slots = max(max(decode_batches), prefill_seqs)
         eng = MubasunEngine(cfg, random_mubasun_weights(cfg, dev, dtype), device=dev, dtype=dtype,
                             kv_pool_tokens=(slots + 1) * (max(prefill_tokens, context) + 256))
-        g = torch.Generator().manual_seed(1)
-        prompts = [torch.randint(0, s["vocab"], (prefill_tokens,), generator=g).tolist() for _ in range(prefill_seqs)]
-        b = eng.new_batcher(slots=slots + 1, max_seq_tokens=max(prefill_tokens, context) + 256)
+        row.update(_measure_ragged(eng, s["vocab"], timer, steps, warmup, peaks, mubasun_work(s, cfg, prefill_tokens, prefill_seqs),
+                                   lambda B: _decode_bytes(s, cfg, B), prefill_tokens, prefill_seqs, context, decode_batches))
+        g = torch.Generator().manual_seed(2)
         T_all = prefill_tokens * prefill_seqs
-
-        def prefill():                                   # all prompts in ONE step of the engine
-            for i in range(prefill_seqs):
-                b.admit(("p", i))
-            b.run_entries([(("p", i), prompts[i], [prefill_tokens - 1]) for i in range(prefill_seqs)])
-
-        def drop():
-            for i in range(prefill_seqs):
-                if ("p", i) in b.slot_of:
-                    b.finish(("p", i))
-        ms = timer.run(prefill, steps, warmup, setup=drop)
-        drop()
-        row["prefill"] = {"tokens": T_all, "sequences": prefill_seqs, "ms": round(_med(ms), 3),
-                          "tok_s": round(T_all / _med(ms) * 1e3), "min_ms": round(min(ms), 3), "max_ms": round(max(ms), 3)}
-        eng._op_timing = True                                    # one more prefill, bracketed op by op
-        for _ in range(2):
-            prefill(); drop(); eng.op_times()
         reps = 3
-        for _ in range(reps):
-            timer.scratch.zero_(); prefill(); drop()
-        times = {k: v / reps for k, v in eng.op_times().items()}
-        eng._op_timing = False
-        row["prefill_ops"] = _roofline(mubasun_work(s, cfg, prefill_tokens, prefill_seqs), times, peaks)
-        row["decode"] = {}
-        for B in decode_batches:
-            for i in range(B):
-                b.admit(("d", i))
-            ctx = torch.randint(0, s["vocab"], (context,), generator=g).tolist()
-            for i in range(B):
-                b.run_entries([(("d", i), ctx, [])])
-            step_ents = [(("d", i), [7 + i], [0]) for i in range(B)]
-            n_dec = min(steps * 4, 200)
-            ms = timer.run(lambda: b.run_entries(step_ents), n_dec, warmup + 2)
-            row["decode"][f"batch{B}"] = {"context": context, "ms_per_step": round(_med(ms), 4),
-                                          "tok_s": round(B / _med(ms) * 1e3), "graph": eng.graph_max_tokens >= B,
-                                          "weight_stream_ms": round(_decode_bytes(s, cfg, B) / (peaks["hbm"] * 1e9) * 1e3, 4)}
-            for i in range(B):
-                b.finish(("d", i))
-        b.close()
-        del eng, b
+        del eng
         torch.cuda.empty_cache()
         # ------------------------------------------------ Gemma decoder at equal size
         gcfg = gemma_config(s)
@@ -347,3 +363,169 @@ def _decode_bytes(s: dict, cfg: dict, B: int) -> float:
             n += min(r["experts"], B * r["top"]) * 3 * D * ml["expert"]["ff"] + 3 * D * ml["shared"]["ff"] + D * (r["experts"] + 2)
     n += D * s["vocab"]
     return 2.0 * n
+
+
+# ------------------------------------------------------------------ Ninisun beside a dense Mubasun of equal size
+NINISUN_SIZES = {
+    # attention layers: heads x dim over kv heads, window + kept first tokens, half of every head rotated, value mixing;
+    # the parallel layer: the same head layout for the sigmoid attention, r_heads x r_dim recurrent heads, decay rank
+    "w1024": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, vdim=128, window=512, keep_first=4, ff=4096,
+                  r_heads=16, r_dim=64, lora=64, vocab=32000),
+    "w2048": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep_first=4, ff=8192,
+                  r_heads=32, r_dim=64, lora=64, vocab=32000),
+}
+
+
+def ninisun_config(s: dict) -> dict:
+    """attention, attention, parallel, attention, ... (every branch of the design is on the path)."""
+    layers = []
+    for i in range(s["layers"]):
+        mlp = {"kind": "dense", "ff": s["ff"]}
+        att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"],
+               "scale": 1.0 / math.sqrt(s["dim"])}
+        if i % 4 == 2:
+            left = dict(att, rot={"dims": s["dim"] // 2, "base": 500000.0,
+                                  "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}})
+            layers.append({"type": "parallel", "mlp": mlp, "mixer": {
+                "left": left, "right": {"heads": s["r_heads"], "dim": s["r_dim"]}, "left_scale": 0.8, "right_scale": 0.5}})
+        else:
+            layers.append({"type": "attention", "mlp": mlp, "mixer": dict(
+                att, rot={"dims": s["dim"] // 2, "base": 1000000.0}, v_mix=True,
+                mask={"size": s["window"], "keep_first": s["keep_first"]})})
+    return {"architecture": "Ninisun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def random_ninisun_weights(cfg: dict, s: dict, device, dtype, seed=0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, out = cfg["width"], {}
+
+    def lin(name, o, i, gain=1.0):
+        out[name] = (torch.randn(o, i, generator=g, device=device) * (gain / math.sqrt(i))).to(dtype)
+
+    def vec(name, n, mean=1.0, std=0.1):
+        out[name] = (mean + std * torch.randn(n, generator=g, device=device)).to(dtype)
+
+    out["embed"] = torch.randn(cfg["vocab"], D, generator=g, device=device).to(dtype)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            vec(p + n, D)
+        vec(p + "ls1", D, 0.5), vec(p + "ls2", D, 0.5)
+        a = m["left"] if L["type"] == "parallel" else m
+        H, G, d, e = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+        q = p + ("mix.left." if L["type"] == "parallel" else "mix.")
+        lin(q + "q", H * d, D), lin(q + "k", G * d, D), lin(q + "v", G * e, D), lin(q + "o", D, H * e)
+        if L["type"] == "parallel":
+            vec(q + "q.b", H * d, 0.0), vec(q + "k.b", G * d, 0.0), vec(q + "v.b", G * e, 0.0), vec(q + "pb", H, -2.0, 0.5)
+            lin(q + "g", H, D)
+            r, nd = p + "mix.right.", m["right"]["heads"] * m["right"]["dim"]
+            for n in ("r", "k", "v", "g", "a"):
+                lin(r + n, nd, D)
+            vec(r + "a.b", nd, 0.0), lin(r + "w1", s["lora"], D), lin(r + "w2", nd, s["lora"]), vec(r + "w0", nd, 0.0, 1.0)
+            vec(r + "norm", nd), lin(r + "o", D, nd)
+        else:
+            out[p + "mix.vmix"] = torch.tensor(0.4, device=device).to(dtype)
+        ff = L["mlp"]["ff"]
+        lin(p + "mlp.gate", ff, D), lin(p + "mlp.up", ff, D), lin(p + "mlp.down", D, ff)
+    vec("final.norm", D)
+    return out
+
+
+def ninisun_work(s: dict, cfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
+    """name -> (FLOPs, bytes) of one step over `seqs` prompts of T1 tokens (bf16 operands, fp32 residual stream)."""
+    T, D, F = T1 * seqs, s["width"], s["ff"]
+    H, G, dim, vdim, W, K0 = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"], s["keep_first"]
+    nd, lora = s["r_heads"] * s["r_dim"], s["lora"]
+    w: Dict[str, List[float]] = {}
+
+    def add(name, flops, nbytes):
+        a = w.setdefault(name, [0.0, 0.0])
+        a[0] += flops
+        a[1] += nbytes
+
+    nq, nk, nv, ng = H * dim, G * dim, G * vdim, H * vdim
+    win_keys = seqs * sum(min(t + 1, W + K0) for t in range(T1))
+    all_keys = seqs * T1 * (T1 + 1) // 2
+    add("norm", 0, T * D * (4 + 2))
+    for L in cfg["layers"]:
+        par = L["type"] == "parallel"
+        npj = nq + nk + nv + ((H + 5 * nd + lora) if par else 0)
+        add("proj", 2 * T * D * npj, 2 * (T * D + npj * D + T * npj))
+        add("rotary_append", 0, 2 * 2 * T * (nq + nk + nv))
+        if par:
+            add("sigmoid_attention", 2 * all_keys * H * (dim + vdim), 2 * T * (nq + ng) + 2 * T * G * (dim + vdim))
+            add("delta_prep", 2 * T * nd * lora, T * (2 * (2 * nd + lora) + 3 * 4 * nd))
+            add("delta_rule", 10 * T * nd * s["r_dim"], T * nd * (3 * 2 + 3 * 4 + 4))
+            add("headnorm_gate", 0, T * nd * (4 + 2 + 2))
+            add("o", 2 * T * (ng + nd) * D, 2 * (T * (ng + nd) + (ng + nd) * D + T * D))
+        else:
+            add("attention", 2 * win_keys * H * (dim + vdim), 2 * T * (nq + ng) + 2 * T * G * (dim + vdim))
+            add("o", 2 * T * ng * D, 2 * (T * ng + ng * D + T * D))
+        add("post_norm", 0, 2 * T * D * (2 + 4 + 4 + 2))
+        add("gate_up", 2 * T * D * 2 * F, 2 * (T * D + 2 * D * F + T * F))
+        add("down", 2 * T * D * F, 2 * (T * F + D * F + T * D))
+    add("head", 2 * seqs * D * s["vocab"], 2 * D * s["vocab"])
+    return {k: (v[0], v[1]) for k, v in w.items()}
+
+
+def _ninisun_decode_bytes(s: dict, cfg: dict) -> float:
+    D, n = s["width"], 0.0
+    nq, nk, nv, ng, nd = s["heads"] * s["dim"], s["kv_heads"] * s["dim"], s["kv_heads"] * s["vdim"], s["heads"] * s["vdim"], \
+        s["r_heads"] * s["r_dim"]
+    for L in cfg["layers"]:
+        n += D * (nq + nk + nv + ng) + 3 * D * s["ff"]
+        if L["type"] == "parallel":
+            n += D * (s["heads"] + 6 * nd + s["lora"]) + nd * s["lora"]
+    return 2.0 * (n + D * s["vocab"])
+
+
+def dense_mubasun_config(s: dict) -> dict:
+    """The closest model of the framework: Mubasun with dense feed-forwards only, same width, depth, heads, window."""
+    layers = [{"type": "attention", "mlp": {"kind": "dense", "ff": s["ff"]},
+               "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"],
+                         "scale": 1.0 / math.sqrt(s["dim"]), "mask": {"size": s["window"]}}} for _ in range(s["layers"])]
+    return {"architecture": "Mubasun", "vocab": s["vocab"], "width": s["width"], "max_positions": MAX_POS,
+            "norm": {"eps": 1e-6, "groups": 4}, "layers": layers}
+
+
+NINISUN_LIKE = [("post_norm", "norm"), ("proj", "proj"), ("rotary_append", "qknorm_append"), ("attention", "attention"),
+                ("sigmoid_attention", "attention"), ("o", "o"), ("gate_up", "dense_up"), ("down", "dense_down"),
+                ("headnorm_gate", "xielu"), ("delta_prep", "qknorm_append"), ("head", "head")]
+
+
+@torch.no_grad()
+def run_ninisun(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, prefill_seqs=4, context=1024,
+                decode_batches=(1, 8)) -> dict:
+    from .mubasun import MubasunEngine
+    from .ninisun import NinisunEngine
+    dev, dtype = torch.device("cuda:0"), torch.bfloat16
+    timer = _Timer()
+    result = {}
+    launches0 = cabi.launch_count()
+    pool = (max(max(decode_batches), prefill_seqs) + 1) * (max(prefill_tokens, context) + 256)
+    for name in sizes:
+        s = NINISUN_SIZES[name]
+        cfg = ninisun_config(s)
+        eng = NinisunEngine(cfg, random_ninisun_weights(cfg, s, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        row = {"size": s}
+        row.update(_measure_ragged(eng, s["vocab"], timer, steps, warmup, peaks, ninisun_work(s, cfg, prefill_tokens, prefill_seqs),
+                                   lambda B: _ninisun_decode_bytes(s, cfg), prefill_tokens, prefill_seqs, context, decode_batches))
+        del eng
+        torch.cuda.empty_cache()
+        ms_ = dict(s, experts=0, top=0, expert_ff=0, shared_ff=0)
+        mcfg = dense_mubasun_config(s)
+        meng = MubasunEngine(mcfg, random_mubasun_weights(mcfg, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        mrow = _measure_ragged(meng, s["vocab"], timer, steps, warmup, peaks, mubasun_work(ms_, mcfg, prefill_tokens, prefill_seqs),
+                               lambda B: _decode_bytes(ms_, mcfg, B), prefill_tokens, prefill_seqs, context, decode_batches)
+        row["mubasun_dense_equal_size"] = mrow
+        cmpr = {}
+        for a, bname in NINISUN_LIKE:
+            if a in row["prefill_ops"] and bname in mrow["prefill_ops"]:
+                fa, fb = row["prefill_ops"][a]["frac"], mrow["prefill_ops"][bname]["frac"]
+                cmpr[a] = {"frac": fa, "like": bname, "like_frac": fb, "distance_ratio": round(fb / fa, 2) if fa > 0 else None}
+        row["like_for_like"] = cmpr
+        result[name] = row
+        del meng
+        torch.cuda.empty_cache()
+    result["gpu_launches"] = int(cabi.launch_count() - launches0)
+    return result

@@ -290,7 +290,7 @@ class NinisunEngine(RaggedEngine):
                                           self.page_size, ptr(inp.slot), ptr(inp.pos), T, self.dt, st), "rotary_append")
         gate = proj[:, at["g"]:] if a.sigmoid else None
         out_scale = w.get("left_scale", 1.0)
-        with tm("attention"):
+        with tm("sigmoid_attention" if a.sigmoid else "attention"):
             if inp.n_tiles and w["attn_tc"]:
                 cabi.check(L.pg_attention_ragged_tc_ex(
                     ptr(att), att.stride(0), ptr(q), q.stride(0), ptr(gate), proj.stride(0), 1 if a.sigmoid else 0, ptr(kp),
