@@ -343,20 +343,22 @@ int pg_postnorm_residual(void* out, float* x, const void* y, int ldy, const void
 /* ---- recurrent mixers: generalised delta rule ---------------------------------------------------------------------
  * Per head, state S [dim x dim] in fp32 per sequence slot ([slots][heads][dim][dim]):
  *   u = k / sqrt(sum(k^2) + key_eps);  S <- diag(w) S - (a * u)(u^T S) + k v^T;  o = S^T r.
- * pg_delta_prep: from the fused projection row (k at k_col0, the removal gate's pre-activation at a_col0, the decay's
- *   inner projection of width `lora` at lora_col0): decay = exp(-decay_scale * sigmoid(W2 tanh(inner) + w0)) with W2
- *   [heads * dim, lora], unit = u, rem = sigmoid(a + a_bias) * u; all fp32 [n_tokens, heads * dim].
+ * pg_delta_prep: from the fused projection row (r, k, v, the removal gate's pre-activation a and the decay's inner
+ *   projection of width `lora` at their column offsets) one packed fp32 record per (token, head):
+ *   [r | k | w | u | a*u | v], each dp = dim rounded up to 4 floats (padding zero), with
+ *   w = exp(-decay_scale * sigmoid(W2 tanh(inner) + w0)) (W2 [heads * dim, lora], product in fp32) and
+ *   a = sigmoid(a + a_bias).  rec holds pg_delta_record_floats(n_tokens, heads, dim) floats.
  * pg_delta_rule: segs (device int32 [n_segs][3] = {state slot, first token row, tokens}; consecutive rows of one
- *   sequence in order; 0 tokens: skipped) are advanced from the slot's state, which is updated in place; r, k, v are
- *   read from the projection row; out fp32 [n_tokens, heads * dim].
+ *   sequence in order; 0 tokens: skipped) are advanced from the slot's state, which is updated in place;
+ *   out fp32 [n_tokens, heads * dim].
  * pg_headnorm_gate: out[t, h*dim + c] = o / sqrt(mean_h(o^2) + eps) * w[h*dim + c] * sigmoid(gate[t, h*dim + c]) *
  *   out_scale, rounded to the model dtype (w, gate may be NULL). */
-int pg_delta_prep(float* decay, float* unit, float* rem, const void* proj, int ld, int k_col0, int a_col0,
-                  int lora_col0, int lora, const void* w2, const void* w0, const void* a_bias, int n_tokens, int heads,
-                  int dim, float decay_scale, float key_eps, int dtype, void* stream);
-int pg_delta_rule(float* out, float* state, const void* proj, int ld, int r_col0, int k_col0, int v_col0,
-                  const float* decay, const float* unit, const float* rem, const int32_t* segs, int n_segs, int heads,
-                  int dim, int dtype, void* stream);
+long long pg_delta_record_floats(int n_tokens, int heads, int dim);
+int pg_delta_prep(float* rec, const void* proj, int ld, int r_col0, int k_col0, int v_col0, int a_col0, int lora_col0,
+                  int lora, const void* w2, const void* w0, const void* a_bias, int n_tokens, int heads, int dim,
+                  float decay_scale, float key_eps, int dtype, void* stream);
+int pg_delta_rule(float* out, float* state, const float* rec, const int32_t* segs, int n_segs, int heads, int dim,
+                  void* stream);
 int pg_headnorm_gate(void* out, int ld_out, const float* o, const void* w, const void* gate, int ld_gate, int n_tokens,
                      int heads, int dim, float eps, float out_scale, int dtype, void* stream);
 

@@ -237,6 +237,53 @@ __global__ void postnorm_residual_kernel(T* __restrict__ out, float* __restrict_
   for (int c = lane; c < D; c += 32) o[c] = from_f<T>(xr[c] * inv_x * to_f<T>(w_next[c]));
 }
 
+// The same for a handful of rows (decode-sized steps): one CTA per row, a thread keeps its PER elements of the row
+// in registers between the statistics and the writes (D <= PER * blockDim.x).
+template <typename T, int PER>
+__global__ void __launch_bounds__(256)
+postnorm_residual_row_kernel(T* __restrict__ out, float* __restrict__ x, const T* __restrict__ y, int ldy,
+                             const T* __restrict__ w_post, const T* __restrict__ scale, const T* __restrict__ w_next,
+                             int D, float eps) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  float wp[PER], sc[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {                  // weights do not depend on the preceding kernel
+    const int c = threadIdx.x + i * blockDim.x;
+    wp[i] = c < D ? to_f<T>(w_post[c]) : 0.f;
+    sc[i] = (c < D && scale) ? to_f<T>(scale[c]) : 1.f;
+  }
+  pdl_wait();
+  const int r = blockIdx.x;
+  const T* yr = y + (size_t)r * ldy;
+  float* xr = x + (size_t)r * D;
+  float yv[PER], xv[PER], ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    yv[i] = c < D ? to_f<T>(yr[c]) : 0.f;
+    xv[i] = c < D ? xr[c] : 0.f;
+    ss += yv[i] * yv[i];
+  }
+  ss = block_sum(ss, red);
+  const float inv_y = 1.f / sqrtf(ss / (float)D + eps);
+  float sx = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    xv[i] += yv[i] * inv_y * wp[i] * sc[i];
+    if (c < D) { xr[c] = xv[i]; sx += xv[i] * xv[i]; }
+  }
+  if (!out) return;
+  sx = block_sum(sx, red);
+  const float inv_x = 1.f / sqrtf(sx / (float)D + eps);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < D) out[(size_t)r * D + c] = from_f<T>(xv[i] * inv_x * to_f<T>(w_next[c]));
+  }
+}
+
 }  // namespace pg
 
 using namespace pg;
@@ -349,6 +396,14 @@ extern "C" int pg_postnorm_residual(void* out, float* x, const void* y, int ldy,
   PG_REQUIRE(x && y && w_post && ldy >= D, "postnorm_residual: x, y and the output-norm weight are needed");
   PG_REQUIRE(!out || w_next, "postnorm_residual: a normalised output needs a weight");
   const int warps = 8;
+  if (rows <= 64 && D <= 16 * 256) {               // decode-sized steps: a CTA per row, the row in registers
+    const int per = D <= 1024 ? 4 : (D <= 2048 ? 8 : 16);
+    PG_DISPATCH_DTYPE(dtype, T, {
+      auto k = per == 4 ? postnorm_residual_row_kernel<T, 4> : (per == 8 ? postnorm_residual_row_kernel<T, 8> : postnorm_residual_row_kernel<T, 16>);
+      return launch_pdl("postnorm_residual", k, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (T*)out, x, (const T*)y, ldy,
+                        (const T*)w_post, (const T*)scale, (const T*)w_next, D, eps);
+    });
+  }
   PG_DISPATCH_DTYPE(dtype, T, {
     return launch_pdl("postnorm_residual", postnorm_residual_kernel<T>, dim3(cdiv(rows, warps)), dim3(warps * 32), 0,
                       (cudaStream_t)stream, (T*)out, x, (const T*)y, ldy, (const T*)w_post, (const T*)scale,

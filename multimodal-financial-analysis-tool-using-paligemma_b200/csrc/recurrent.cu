@@ -7,14 +7,19 @@
 // Everything that enters the recurrence besides the projections themselves is fp32: the decay w, the removal rate a,
 // the unit key u, the state and the output.
 //
-// delta_prep_kernel   (CTA per token)   : w = exp(-decay_scale * sigmoid(W2 tanh(lora) + w0)), a = sigmoid(a_pre + a_bias),
-//                                         u; writes w, u and a * u as fp32 rows.
-// delta_rule_kernel   (warp per (sequence segment, head, 32 value columns)): a lane owns one value column of the state
-//                                         in registers; the u^T S and S^T r products are then per-lane dot products
-//                                         with vectors that all lanes read from shared memory, so the tokens of a
-//                                         segment need no cross-lane traffic at all.  Token inputs are staged in
-//                                         chunks.  The state is loaded from / stored to the slot's state once per
-//                                         launch, which makes a prompt portion and a single decoded token the same case.
+// delta_prep_kernel   (CTA per 8 tokens) : w = exp(-decay_scale * sigmoid(W2 tanh(inner) + w0)) with the W2 product in
+//                                         fp32 (a thread owns a channel and walks its W2 row once for the CTA's
+//                                         tokens), a = sigmoid(a_pre + a_bias), u; writes one packed fp32 record
+//                                         [r | k | w | u | a*u | v] x dp (dp = dim rounded up to 4) per (token, head),
+//                                         so that the recurrence streams ONE contiguous block per token and head.
+// delta_rule_kernel   (CTA per (sequence segment, head)): the state lives in registers, a thread owning a quarter of
+//                                         one value column; the u^T S and S^T r products are per-thread dot products
+//                                         with vectors read from shared memory plus two shuffle steps, so the tokens
+//                                         of a segment need no block-wide exchange.  The records of the next
+//                                         tokens arrive by cp.async into the other half of a double buffer while
+//                                         the current ones are consumed.  The state is loaded from / stored to the
+//                                         slot's state once per launch, which makes a prompt portion and a single
+//                                         decoded token the same case.
 // headnorm_gate_kernel (warp per (token, head)): o / rms(o) per head, times a weight, times sigmoid(gate), times a
 //                                         constant, rounded to the model dtype as the output projection's operand.
 #include "common.cuh"
@@ -23,110 +28,190 @@ namespace pg {
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
+constexpr int PREP_TOK = 8;     // tokens per CTA of the prep kernel
+constexpr int REC_VECS = 6;     // r, k, w, u, a*u, v
+enum { REC_R = 0, REC_K = 1, REC_W = 2, REC_U = 3, REC_AU = 4, REC_V = 5 };
+
 template <typename T>
-__global__ void delta_prep_kernel(float* __restrict__ decay, float* __restrict__ unit, float* __restrict__ rem,
-                                  const T* __restrict__ proj, int ld, int k_col0, int a_col0, int lora_col0, int lora,
-                                  const T* __restrict__ w2, const T* __restrict__ w0, const T* __restrict__ a_bias,
-                                  int heads, int dim, float decay_scale, float key_eps) {
-  extern __shared__ float sm[];           // [lora] tanh of the decay's inner projection | [heads] sum of k^2
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(float* __restrict__ rec, const T* __restrict__ proj, int ld, int r_col0, int k_col0, int v_col0,
+                  int a_col0, int lora_col0, int lora, const T* __restrict__ w2, const T* __restrict__ w0,
+                  const T* __restrict__ a_bias, int n_tokens, int heads, int dim, int dp, float decay_scale,
+                  float key_eps) {
+  extern __shared__ float sm[];           // [PREP_TOK][lora] tanh of the decay's inner projection | [PREP_TOK][heads] sum k^2
   float* lo = sm;
-  float* ksq = sm + lora;
+  float* ksq = sm + PREP_TOK * lora;
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, nd = heads * dim;
-  const T* row = proj + (size_t)t * ld;
-  for (int j = threadIdx.x; j < lora; j += blockDim.x) lo[j] = tanhf(to_f<T>(row[lora_col0 + j]));
+  const int t0 = blockIdx.x * PREP_TOK, nt = min(PREP_TOK, n_tokens - t0), nd = heads * dim;
+  for (int idx = threadIdx.x; idx < PREP_TOK * lora; idx += blockDim.x) {
+    const int tt = idx / lora, j = idx % lora;
+    lo[idx] = tt < nt ? tanhf(to_f<T>(proj[(size_t)(t0 + tt) * ld + lora_col0 + j])) : 0.f;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int h = warp; h < heads; h += warps) {
+  for (int item = warp; item < nt * heads; item += warps) {
+    const int tt = item / heads, h = item % heads;
+    const T* kr = proj + (size_t)(t0 + tt) * ld + k_col0 + h * dim;
     float s = 0.f;
-    for (int c = lane; c < dim; c += 32) { const float v = to_f<T>(row[k_col0 + h * dim + c]); s += v * v; }
+    for (int c = lane; c < dim; c += 32) { const float v = to_f<T>(kr[c]); s += v * v; }
     s = warp_sum(s);
-    if (lane == 0) ksq[h] = s;
+    if (lane == 0) ksq[tt * heads + h] = s;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < nd; c += blockDim.x) {
-    float z = to_f<T>(w0[c]);
+  constexpr int V = Vec<T>::N;
+  const bool vec = (lora % V) == 0 && (reinterpret_cast<uintptr_t>(w2) & 15) == 0;
+  // blockIdx.y cuts the channels into slices of c_per (a handful of tokens: more CTAs than token groups)
+  const int c_per = (nd + gridDim.y - 1) / gridDim.y, c_end = min(nd, (int)(blockIdx.y + 1) * c_per);
+  for (int c = blockIdx.y * c_per + threadIdx.x; c < c_end; c += blockDim.x) {
+    float z[PREP_TOK];
+    const float z0 = to_f<T>(w0[c]);
+#pragma unroll
+    for (int tt = 0; tt < PREP_TOK; ++tt) z[tt] = z0;
     const T* wr = w2 + (size_t)c * lora;
-    for (int j = 0; j < lora; ++j) z = fmaf(to_f<T>(wr[j]), lo[j], z);
-    const float w = expf(-decay_scale * sigmoid_f(z));
-    float a = to_f<T>(row[a_col0 + c]);
-    if (a_bias) a += to_f<T>(a_bias[c]);
-    a = sigmoid_f(a);
-    const float u = to_f<T>(row[k_col0 + c]) / sqrtf(ksq[c / dim] + key_eps);
-    const size_t o = (size_t)t * nd + c;
-    decay[o] = w;
-    unit[o] = u;
-    rem[o] = a * u;
+    if (vec) {
+      for (int j = 0; j < lora; j += V) {
+        float f[V];
+        unpack<T>(*reinterpret_cast<const uint4*>(wr + j), f);
+#pragma unroll
+        for (int tt = 0; tt < PREP_TOK; ++tt)
+#pragma unroll
+          for (int i = 0; i < V; ++i) z[tt] = fmaf(f[i], lo[tt * lora + j + i], z[tt]);
+      }
+    } else {
+      for (int j = 0; j < lora; ++j) {
+        const float f = to_f<T>(wr[j]);
+#pragma unroll
+        for (int tt = 0; tt < PREP_TOK; ++tt) z[tt] = fmaf(f, lo[tt * lora + j], z[tt]);
+      }
+    }
+    const int h = c / dim, i = c % dim;
+    const float ab = a_bias ? to_f<T>(a_bias[c]) : 0.f;
+#pragma unroll
+    for (int tt = 0; tt < PREP_TOK; ++tt) {
+      if (tt >= nt) break;
+      const T* row = proj + (size_t)(t0 + tt) * ld;
+      const float k = to_f<T>(row[k_col0 + c]);
+      const float u = k / sqrtf(ksq[tt * heads + h] + key_eps);
+      float* o = rec + (((size_t)(t0 + tt) * heads + h) * REC_VECS) * dp + i;
+      o[REC_R * dp] = to_f<T>(row[r_col0 + c]);
+      o[REC_K * dp] = k;
+      o[REC_W * dp] = expf(-decay_scale * sigmoid_f(z[tt]));
+      o[REC_U * dp] = u;
+      o[REC_AU * dp] = sigmoid_f(to_f<T>(row[a_col0 + c]) + ab) * u;
+      o[REC_V * dp] = to_f<T>(row[v_col0 + c]);
+    }
   }
+  // the padding columns of every record are zero, so the recurrence can run whole 4-wide groups
+  const int pad = dp - dim;
+  if (pad && blockIdx.y == 0)
+    for (int idx = threadIdx.x; idx < nt * heads * REC_VECS * pad; idx += blockDim.x) {
+      const int i = dim + idx % pad, which = idx / pad;
+      rec[((size_t)t0 * heads * REC_VECS + which) * dp + i] = 0.f;
+    }
 }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // segs: [n_segs][3] = {state slot, first token row, tokens}; the tokens of a segment are consecutive rows of one
 // sequence in position order.  A segment with 0 tokens is skipped (the list is padded to a fixed length so that a
-// captured launch stays valid).
-template <typename T, int DMAX, int CH>
-__global__ void __launch_bounds__(32)
-delta_rule_kernel(float* __restrict__ out, float* __restrict__ state, const T* __restrict__ proj, int ld, int r_col0,
-                  int k_col0, int v_col0, const float* __restrict__ decay, const float* __restrict__ unit,
-                  const float* __restrict__ rem, const int32_t* __restrict__ segs, int heads, int dim) {
-  __shared__ __align__(16) float sh[CH][5][DMAX];   // r, k, w, u, a*u of CH tokens
-  __shared__ float sv[CH][32];                      // this warp's 32 value columns
+// captured launch stays valid).  Shared memory: two buffers of CH records.
+template <int DMAX, int CH>
+__global__ void __launch_bounds__(DMAX * 4)
+delta_rule_kernel(float* __restrict__ out, float* __restrict__ state, const float* __restrict__ rec,
+                  const int32_t* __restrict__ segs, int heads, int dim, int dp) {
+  // thread = (value column j, row group rg): of column j it keeps the rows 4 (m RG + rg) + e (m < NG, e < 4) in
+  // registers, i.e. every RG-th group of four rows, so that the four row groups of a column (adjacent lanes) read four
+  // consecutive 16-byte pieces of a vector (no bank conflict) and the two column sums of a token are two shuffle
+  // steps each.  Vectors sit in shared memory with stride DMAX and zeros behind dim: no bound checks in the token loop.
+  constexpr int RG = 4, NG = DMAX / (4 * RG);
+  extern __shared__ __align__(16) float sh[];       // [2][CH][REC_VECS][DMAX]
   pdl_launch_dependents();
   pdl_wait();
   const int32_t* sg = segs + 3 * (size_t)blockIdx.x;
   const int slot = sg[0], row0 = sg[1], n = sg[2];
   if (n <= 0) return;
-  const int h = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane, nd = heads * dim;
+  const int h = blockIdx.y, j = threadIdx.x / RG, rg = threadIdx.x % RG, nd = heads * dim;
   const bool live = j < dim;
-  float S[DMAX];
+  constexpr int RSZ = REC_VECS * DMAX;              // floats of one record in shared memory
+  if (dp < DMAX)
+    for (int idx = threadIdx.x; idx < 2 * CH * RSZ; idx += blockDim.x)
+      if (idx % DMAX >= dp) sh[idx] = 0.f;
+  float S[NG * 4];
   float* st = state + ((size_t)slot * heads + h) * dim * dim;
 #pragma unroll
-  for (int i = 0; i < DMAX; ++i) S[i] = (live && i < dim) ? st[(size_t)i * dim + j] : 0.f;
-  for (int t0 = 0; t0 < n; t0 += CH) {
-    const int nt = min(CH, n - t0);
-    __syncwarp();
-    for (int idx = lane; idx < nt * DMAX; idx += 32) {
-      const int tt = idx / DMAX, c = idx % DMAX;
-      const size_t trow = (size_t)row0 + t0 + tt;
-      const bool in = c < dim;
-      const size_t o = trow * nd + h * dim + c;
-      sh[tt][0][c] = in ? to_f<T>(proj[trow * ld + r_col0 + h * dim + c]) : 0.f;
-      sh[tt][1][c] = in ? to_f<T>(proj[trow * ld + k_col0 + h * dim + c]) : 0.f;
-      sh[tt][2][c] = in ? decay[o] : 0.f;
-      sh[tt][3][c] = in ? unit[o] : 0.f;
-      sh[tt][4][c] = in ? rem[o] : 0.f;
-    }
-    for (int tt = 0; tt < nt; ++tt)
-      sv[tt][lane] = live ? to_f<T>(proj[((size_t)row0 + t0 + tt) * ld + v_col0 + h * dim + j]) : 0.f;
-    __syncwarp();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float vj = sv[tt][lane];
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;            // u^T S over this lane's column
+  for (int m = 0; m < NG; ++m)
 #pragma unroll
-      for (int i = 0; i < DMAX; i += 4) {
-        const float4 u4 = *reinterpret_cast<const float4*>(&sh[tt][3][i]);
-        d0 = fmaf(u4.x, S[i], d0); d1 = fmaf(u4.y, S[i + 1], d1); d2 = fmaf(u4.z, S[i + 2], d2); d3 = fmaf(u4.w, S[i + 3], d3);
+    for (int e = 0; e < 4; ++e) {
+      const int i = 4 * (m * RG + rg) + e;
+      S[m * 4 + e] = (live && i < dim) ? st[(size_t)i * dim + j] : 0.f;
+    }
+  const int vp = dp / 4, pieces = REC_VECS * vp;    // 16-byte pieces of one vector / one record
+  auto fetch = [&](int t0, int buf) {               // records of tokens [t0, t0 + CH) of this head -> buffer buf
+    const int nt = min(CH, n - t0);
+    for (int idx = threadIdx.x; idx < nt * pieces; idx += blockDim.x) {
+      const int tt = idx / pieces, rem = idx % pieces, v = rem / vp, pc = rem % vp;
+      cp_async16(sh + ((size_t)buf * CH + tt) * RSZ + v * DMAX + pc * 4,
+                 rec + (((size_t)row0 + t0 + tt) * heads + h) * (size_t)(REC_VECS * dp) + v * dp + pc * 4);
+    }
+    cp_async_commit();
+  };
+  fetch(0, 0);
+  int buf = 0;
+  for (int t0 = 0; t0 < n; t0 += CH, buf ^= 1) {
+    const int nt = min(CH, n - t0);
+    if (t0 + CH < n) { fetch(t0 + CH, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+#pragma unroll 2
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* r = sh + ((size_t)buf * CH + tt) * RSZ + 4 * rg;
+      const float vj = r[REC_V * DMAX + j - 4 * rg];
+      float4 u4[NG], w4[NG], a4[NG], k4[NG], r4[NG];
+#pragma unroll
+      for (int m = 0; m < NG; ++m) {
+        u4[m] = *reinterpret_cast<const float4*>(r + REC_U * DMAX + 16 * m);
+        w4[m] = *reinterpret_cast<const float4*>(r + REC_W * DMAX + 16 * m);
+        a4[m] = *reinterpret_cast<const float4*>(r + REC_AU * DMAX + 16 * m);
+        k4[m] = *reinterpret_cast<const float4*>(r + REC_K * DMAX + 16 * m);
+        r4[m] = *reinterpret_cast<const float4*>(r + REC_R * DMAX + 16 * m);
       }
-      const float us = (d0 + d1) + (d2 + d3);
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;            // this thread's part of u^T S for column j
+#pragma unroll
+      for (int m = 0; m < NG; ++m) {
+        d0 = fmaf(u4[m].x, S[4 * m], d0); d1 = fmaf(u4[m].y, S[4 * m + 1], d1);
+        d2 = fmaf(u4[m].z, S[4 * m + 2], d2); d3 = fmaf(u4[m].w, S[4 * m + 3], d3);
+      }
+      float us = (d0 + d1) + (d2 + d3);
+      us += __shfl_xor_sync(0xffffffffu, us, 1);
+      us += __shfl_xor_sync(0xffffffffu, us, 2);
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DMAX; i += 4) {
-        const float4 w4 = *reinterpret_cast<const float4*>(&sh[tt][2][i]);
-        const float4 a4 = *reinterpret_cast<const float4*>(&sh[tt][4][i]);
-        const float4 k4 = *reinterpret_cast<const float4*>(&sh[tt][1][i]);
-        const float4 r4 = *reinterpret_cast<const float4*>(&sh[tt][0][i]);
-        S[i] = fmaf(k4.x, vj, fmaf(-a4.x, us, w4.x * S[i]));
-        S[i + 1] = fmaf(k4.y, vj, fmaf(-a4.y, us, w4.y * S[i + 1]));
-        S[i + 2] = fmaf(k4.z, vj, fmaf(-a4.z, us, w4.z * S[i + 2]));
-        S[i + 3] = fmaf(k4.w, vj, fmaf(-a4.w, us, w4.w * S[i + 3]));
-        o0 = fmaf(r4.x, S[i], o0); o1 = fmaf(r4.y, S[i + 1], o1); o2 = fmaf(r4.z, S[i + 2], o2); o3 = fmaf(r4.w, S[i + 3], o3);
+      for (int m = 0; m < NG; ++m) {
+        S[4 * m] = fmaf(k4[m].x, vj, fmaf(-a4[m].x, us, w4[m].x * S[4 * m]));
+        S[4 * m + 1] = fmaf(k4[m].y, vj, fmaf(-a4[m].y, us, w4[m].y * S[4 * m + 1]));
+        S[4 * m + 2] = fmaf(k4[m].z, vj, fmaf(-a4[m].z, us, w4[m].z * S[4 * m + 2]));
+        S[4 * m + 3] = fmaf(k4[m].w, vj, fmaf(-a4[m].w, us, w4[m].w * S[4 * m + 3]));
+        o0 = fmaf(r4[m].x, S[4 * m], o0); o1 = fmaf(r4[m].y, S[4 * m + 1], o1);
+        o2 = fmaf(r4[m].z, S[4 * m + 2], o2); o3 = fmaf(r4[m].w, S[4 * m + 3], o3);
       }
-      if (live) out[((size_t)row0 + t0 + tt) * nd + h * dim + j] = (o0 + o1) + (o2 + o3);
+      float o = (o0 + o1) + (o2 + o3);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (live && rg == 0) out[((size_t)row0 + t0 + tt) * nd + h * dim + j] = o;
     }
+    __syncthreads();                                // every thread is done with this buffer before it is refilled
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i)
-      if (i < dim) st[(size_t)i * dim + j] = S[i];
+    for (int m = 0; m < NG; ++m)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 4 * (m * RG + rg) + e;
+        if (i < dim) st[(size_t)i * dim + j] = S[m * 4 + e];
+      }
   }
 }
 
@@ -153,46 +238,50 @@ __global__ void headnorm_gate_kernel(T* __restrict__ out, int ld_out, const floa
   }
 }
 
-template <typename T, int DMAX, int CH>
-static int launch_delta(float* out, float* state, const void* proj, int ld, int r_col0, int k_col0, int v_col0,
-                        const float* decay, const float* unit, const float* rem, const int32_t* segs, int n_segs,
-                        int heads, int dim, cudaStream_t st) {
-  return launch_pdl("delta_rule", delta_rule_kernel<T, DMAX, CH>, dim3(n_segs, heads, cdiv(dim, 32)), dim3(32), 0, st, out,
-                    state, (const T*)proj, ld, r_col0, k_col0, v_col0, decay, unit, rem, segs, heads, dim);
+template <int DMAX, int CH>
+static int launch_delta(float* out, float* state, const float* rec, const int32_t* segs, int n_segs, int heads, int dim,
+                        cudaStream_t st) {
+  const int dp = (dim + 3) / 4 * 4;
+  const size_t smem = sizeof(float) * 2 * CH * REC_VECS * DMAX;
+  return launch_pdl("delta_rule", delta_rule_kernel<DMAX, CH>, dim3(n_segs, heads), dim3(DMAX * 4), smem, st, out, state, rec, segs,
+                    heads, dim, dp);
 }
 
 }  // namespace pg
 
 using namespace pg;
 
-extern "C" int pg_delta_prep(float* decay, float* unit, float* rem, const void* proj, int ld, int k_col0, int a_col0,
+extern "C" long long pg_delta_record_floats(int n_tokens, int heads, int dim) {
+  return (long long)n_tokens * heads * REC_VECS * ((dim + 3) / 4 * 4);
+}
+
+extern "C" int pg_delta_prep(float* rec, const void* proj, int ld, int r_col0, int k_col0, int v_col0, int a_col0,
                              int lora_col0, int lora, const void* w2, const void* w0, const void* a_bias, int n_tokens,
                              int heads, int dim, float decay_scale, float key_eps, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
-  PG_REQUIRE(decay && unit && rem && proj && w2 && w0 && lora > 0 && heads > 0 && dim > 0, "delta_prep: bad arguments");
-  const size_t smem = sizeof(float) * ((size_t)lora + heads);
+  PG_REQUIRE(rec && proj && w2 && w0 && lora > 0 && heads > 0 && dim > 0, "delta_prep: bad arguments");
+  const size_t smem = sizeof(float) * PREP_TOK * ((size_t)lora + heads);
   PG_DISPATCH_DTYPE(dtype, T, {
-    return launch_pdl("delta_prep", delta_prep_kernel<T>, dim3(n_tokens), dim3(heads * dim >= 1024 ? 256 : 128), smem,
-                      (cudaStream_t)stream, decay, unit, rem, (const T*)proj, ld, k_col0, a_col0, lora_col0, lora,
-                      (const T*)w2, (const T*)w0, (const T*)a_bias, heads, dim, decay_scale, key_eps);
+    const int threads = heads * dim >= 256 ? 256 : 128;
+    const int slices = n_tokens <= 64 ? cdiv(heads * dim, threads) : 1;
+    return launch_pdl("delta_prep", delta_prep_kernel<T>, dim3(cdiv(n_tokens, PREP_TOK), slices), dim3(threads),
+                      smem, (cudaStream_t)stream, rec, (const T*)proj, ld, r_col0, k_col0, v_col0, a_col0, lora_col0, lora,
+                      (const T*)w2, (const T*)w0, (const T*)a_bias, n_tokens, heads, dim, (dim + 3) / 4 * 4, decay_scale,
+                      key_eps);
   });
   return PG_OK;
 }
 
-extern "C" int pg_delta_rule(float* out, float* state, const void* proj, int ld, int r_col0, int k_col0, int v_col0,
-                             const float* decay, const float* unit, const float* rem, const int32_t* segs, int n_segs,
-                             int heads, int dim, int dtype, void* stream) {
+extern "C" int pg_delta_rule(float* out, float* state, const float* rec, const int32_t* segs, int n_segs, int heads,
+                             int dim, void* stream) {
   if (n_segs <= 0) return PG_OK;
-  PG_REQUIRE(out && state && proj && decay && unit && rem && segs, "delta_rule: bad arguments");
+  PG_REQUIRE(out && state && rec && segs, "delta_rule: bad arguments");
   PG_REQUIRE(dim > 0 && dim <= 256, "delta_rule: head size %d (1..256)", dim);
   cudaStream_t st = (cudaStream_t)stream;
-  PG_DISPATCH_DTYPE(dtype, T, {
-    if (dim <= 32) return launch_delta<T, 32, 8>(out, state, proj, ld, r_col0, k_col0, v_col0, decay, unit, rem, segs, n_segs, heads, dim, st);
-    if (dim <= 64) return launch_delta<T, 64, 8>(out, state, proj, ld, r_col0, k_col0, v_col0, decay, unit, rem, segs, n_segs, heads, dim, st);
-    if (dim <= 128) return launch_delta<T, 128, 8>(out, state, proj, ld, r_col0, k_col0, v_col0, decay, unit, rem, segs, n_segs, heads, dim, st);
-    return launch_delta<T, 256, 4>(out, state, proj, ld, r_col0, k_col0, v_col0, decay, unit, rem, segs, n_segs, heads, dim, st);
-  });
-  return PG_OK;
+  if (dim <= 32) return launch_delta<32, 8>(out, state, rec, segs, n_segs, heads, dim, st);
+  if (dim <= 64) return launch_delta<64, 8>(out, state, rec, segs, n_segs, heads, dim, st);
+  if (dim <= 128) return launch_delta<128, 4>(out, state, rec, segs, n_segs, heads, dim, st);
+  return launch_delta<256, 2>(out, state, rec, segs, n_segs, heads, dim, st);
 }
 
 extern "C" int pg_headnorm_gate(void* out, int ld_out, const float* o, const void* w, const void* gate, int ld_gate,

@@ -81,8 +81,9 @@ SIGNATURES = {
     "pg_rotary_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _f, _i, _vp, _i, _f, _vp, _vp,
                          _vp, _i, _i, _vp, _vp, _i, _i, _vp],
     "pg_postnorm_residual": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _f, _i, _vp],
-    "pg_delta_prep": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f, _i, _vp],
-    "pg_delta_rule": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pg_delta_record_floats": [_i, _i, _i],
+    "pg_delta_prep": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f, _i, _vp],
+    "pg_delta_rule": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "pg_headnorm_gate": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _vp],
     "pg_moe_route": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "pg_moe_sort": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -90,7 +91,8 @@ SIGNATURES = {
     "pg_gather_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "pg_moe_combine": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp],
 }
-_RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll}
+_RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll,
+            "pg_delta_record_floats": _ll}
 
 _lib = None
 

@@ -454,8 +454,8 @@ def ninisun_work(s: dict, cfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
         add("rotary_append", 0, 2 * 2 * T * (nq + nk + nv))
         if par:
             add("sigmoid_attention", 2 * all_keys * H * (dim + vdim), 2 * T * (nq + ng) + 2 * T * G * (dim + vdim))
-            add("delta_prep", 2 * T * nd * lora, T * (2 * (2 * nd + lora) + 3 * 4 * nd))
-            add("delta_rule", 10 * T * nd * s["r_dim"], T * nd * (3 * 2 + 3 * 4 + 4))
+            add("delta_prep", 2 * T * nd * lora, T * (2 * (4 * nd + lora) + 6 * 4 * nd))     # six fp32 vectors per head out
+            add("delta_rule", 10 * T * nd * s["r_dim"], T * nd * (6 * 4 + 4))                # fp32 FMAs, not tensor work
             add("headnorm_gate", 0, T * nd * (4 + 2 + 2))
             add("o", 2 * T * (ng + nd) * D, 2 * (T * (ng + nd) + (ng + nd) * D + T * D))
         else:

@@ -312,16 +312,15 @@ class NinisunEngine(RaggedEngine):
         nd = w["nd"]
         if kv.state is None or li not in kv.state.layers:
             raise RuntimeError("this step's slot table carries no recurrent state for the model's recurrent layers")
-        dec, unit, rem = (self._new(T, nd, dtype=torch.float32) for _ in range(3))
+        rec = self._new(int(L.pg_delta_record_floats(T, d.heads, d.dim)), dtype=torch.float32)
         with tm("delta_prep"):
-            cabi.check(L.pg_delta_prep(ptr(dec), ptr(unit), ptr(rem), ptr(proj), proj.stride(0), at["rk"], at["ra"], at["rw1"],
+            cabi.check(L.pg_delta_prep(ptr(rec), ptr(proj), proj.stride(0), at["rr"], at["rk"], at["rv"], at["ra"], at["rw1"],
                                        w["lora"], ptr(w["w2"]), ptr(w["w0"]), ptr(w["ab"]), T, d.heads, d.dim, DECAY_SCALE,
                                        KEY_EPS, self.dt, st), "delta_prep")
         o = self._new(T, nd, dtype=torch.float32)
         with tm("delta_rule"):
-            cabi.check(L.pg_delta_rule(ptr(o), ptr(kv.state.layers[li]), ptr(proj), proj.stride(0), at["rr"], at["rk"], at["rv"],
-                                       ptr(dec), ptr(unit), ptr(rem), ptr(inp.segs), inp.n_segs, d.heads, d.dim, self.dt, st),
-                       "delta_rule")
+            cabi.check(L.pg_delta_rule(ptr(o), ptr(kv.state.layers[li]), ptr(rec), ptr(inp.segs), inp.n_segs, d.heads, d.dim,
+                                       st), "delta_rule")
         with tm("headnorm_gate"):
             cabi.check(L.pg_headnorm_gate(ptr(att[:, w["r_col"]:]), att.stride(0), ptr(o), ptr(w["rnorm"]),
                                           ptr(proj[:, at["rg"]:]), proj.stride(0), T, d.heads, d.dim, self.cfg.eps,

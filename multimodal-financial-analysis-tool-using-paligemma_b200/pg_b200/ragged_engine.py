@@ -22,6 +22,7 @@ import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from . import _cabi as cabi
@@ -125,23 +126,19 @@ class RaggedEngine(PagePool):
 
     # ------------------------------------------------------------------ one step
     @staticmethod
-    def _segments(slots: Sequence[int], positions: Sequence[int]) -> List[int]:
-        """{slot, first row, tokens} of every run of one sequence's tokens; a sequence has ONE run per step."""
-        segs: List[int] = []
-        seen = set()
-        t0, T = 0, len(slots)
-        while t0 < T:
-            t1 = t0 + 1
-            while t1 < T and slots[t1] == slots[t0]:
-                if positions[t1] != positions[t1 - 1] + 1:
-                    raise ValueError("the tokens of a sequence must sit at consecutive positions within a step")
-                t1 += 1
-            if slots[t0] in seen:
-                raise ValueError("the tokens of a sequence must be consecutive rows of a step")
-            seen.add(slots[t0])
-            segs += [int(slots[t0]), t0, t1 - t0]
-            t0 = t1
-        return segs
+    def _runs(slots: np.ndarray, positions: np.ndarray):
+        """Starts of the runs of consecutive tokens of one sequence at consecutive positions (and the end)."""
+        T = slots.shape[0]
+        brk = np.flatnonzero((slots[1:] != slots[:-1]) | (positions[1:] != positions[:-1] + 1)) + 1
+        return np.concatenate(([0], brk, [T]))
+
+    @staticmethod
+    def _segments(slots: np.ndarray, bounds: np.ndarray) -> List[int]:
+        """{slot, first row, tokens} per sequence; a sequence has ONE run of consecutive positions per step."""
+        first = slots[bounds[:-1]]
+        if np.unique(first).shape[0] != first.shape[0]:
+            raise ValueError("the tokens of a sequence must be consecutive rows at consecutive positions of a step")
+        return np.stack([first, bounds[:-1], np.diff(bounds)], 1).reshape(-1).tolist()
 
     @torch.no_grad()
     def forward_tokens(self, kv, ids: Sequence[int], slots: Sequence[int], positions: Sequence[int],
@@ -156,27 +153,25 @@ class RaggedEngine(PagePool):
             return torch.empty((0, self.cfg.vocab), dtype=torch.float32, device=self.device)
         if self.max_positions is not None and max(positions) >= self.max_positions:
             raise ValueError(f"position {max(positions)} exceeds max_positions {self.max_positions}")
+        slots_np, pos_np = np.asarray(slots, dtype=np.int64), np.asarray(positions, dtype=np.int64)
+        bounds = self._runs(slots_np, pos_np)
         segs: List[int] = []
         if self.needs_segments:
-            segs = self._segments(slots, positions)
+            segs = self._segments(slots_np, bounds)
             n_max = min(T, int(kv.page_table.shape[0]))
             segs += [0, 0, 0] * (n_max - len(segs) // 3)
         ns = len(segs) // 3
         # query tiles of the tensor-core attention: runs of <= 128 consecutive tokens of one sequence
         tiles: List[int] = []
         if T >= self.attn_tc_min_tokens and self._attn_tc_any:
-            t0 = 0
-            while t0 < T:
-                t1 = t0 + 1
-                while t1 < T and t1 - t0 < 128 and slots[t1] == slots[t0] and positions[t1] == positions[t1 - 1] + 1:
-                    t1 += 1
-                tiles += [t0, t1 - t0, int(slots[t0]), int(positions[t0])]
-                t0 = t1
+            for r0, r1 in zip(bounds[:-1].tolist(), bounds[1:].tolist()):
+                for t0 in range(r0, r1, 128):
+                    tiles += [t0, min(128, r1 - t0), int(slots_np[t0]), int(pos_np[t0])]
         nt = len(tiles) // 4
         host = torch.empty(4 * T + nw + 3 * ns + 4 * nt, dtype=torch.int32).pin_memory()
-        host[:2 * T].view(torch.int64).copy_(torch.as_tensor(ids, dtype=torch.int64))
-        host[2 * T:3 * T].copy_(torch.as_tensor(slots, dtype=torch.int32))
-        host[3 * T:4 * T].copy_(torch.as_tensor(positions, dtype=torch.int32))
+        host[:2 * T].view(torch.int64).copy_(torch.from_numpy(np.asarray(ids, dtype=np.int64)))
+        host[2 * T:3 * T].copy_(torch.from_numpy(slots_np))
+        host[3 * T:4 * T].copy_(torch.from_numpy(pos_np))
         if nw:
             host[4 * T:4 * T + nw].copy_(torch.as_tensor(want_rows, dtype=torch.int32))
         if ns:

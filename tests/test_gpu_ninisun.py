@@ -62,17 +62,19 @@ CT = {torch.float32: 0, torch.bfloat16: 1}
 
 
 # ------------------------------------------------------------------ mechanisms alone (C ABI)
-@pytest.mark.parametrize("D,with_scale,with_next", [(48, True, True), (100, False, True), (256, True, False)])
-def test_output_norm_layer_scale_residual_next_norm(D, with_scale, with_next):
+@pytest.mark.parametrize("D,with_scale,with_next", [(48, True, True), (100, False, True), (256, True, False),
+                                                    (1500, True, True), (4096, True, True), (4100, False, True)])
+@pytest.mark.parametrize("R", [9, 70])       # a CTA per row for a handful of rows, a warp per row beyond
+def test_output_norm_layer_scale_residual_next_norm(D, with_scale, with_next, R):
     cabi, L, st = _lib()
     g = torch.Generator().manual_seed(2)
-    x, y = torch.randn(9, D, generator=g) * 2, torch.randn(9, D + 8, generator=g) * 5
+    x, y = torch.randn(R, D, generator=g) * 2, torch.randn(R, D + 8, generator=g) * 5
     wp, sc, wn = (torch.randn(D, generator=g) for _ in range(3))
-    xd, yd, out = x.cuda(), y.cuda(), torch.zeros(9, D, device="cuda")
+    xd, yd, out = x.cuda(), y.cuda(), torch.zeros(R, D, device="cuda")
     wpd, scd, wnd = wp.cuda(), sc.cuda(), wn.cuda()
     cabi.check(L.pg_postnorm_residual(out.data_ptr() if with_next else None, xd.data_ptr(), yd.data_ptr(), D + 8,
                                       wpd.data_ptr(), scd.data_ptr() if with_scale else None,
-                                      wnd.data_ptr() if with_next else None, 9, D, 1e-3, cabi.PG_F32, st))
+                                      wnd.data_ptr() if with_next else None, R, D, 1e-3, cabi.PG_F32, st))
     want = x.to(F64) + O.rms_norm(y[:, :D], wp, 1e-3) * (sc.to(F64) if with_scale else 1.0)
     _close(xd, want, 1e-6)
     if with_next:
@@ -296,26 +298,28 @@ def test_delta_rule_prep_recurrence_head_norm(heads, dim, lora):
     state0 = torch.randn(4, heads, dim, dim, generator=g) * 0.3
     state = state0.clone().cuda()
     projd = proj.cuda()
-    dec, unit, rem, o = (torch.empty(T, nd, device="cuda") for _ in range(4))
+    o = torch.empty(T, nd, device="cuda")
+    rec = torch.empty(int(L.pg_delta_record_floats(T, heads, dim)), device="cuda")
     dw = [t.cuda() for t in (w2, w0, ab, nw)]
-    cabi.check(L.pg_delta_prep(dec.data_ptr(), unit.data_ptr(), rem.data_ptr(), projd.data_ptr(), ld, c_k, c_a, c_l, lora,
-                               dw[0].data_ptr(), dw[1].data_ptr(), dw[2].data_ptr(), T, heads, dim, math.exp(-0.5), 1e-6,
-                               cabi.PG_F32, st))
+    cabi.check(L.pg_delta_prep(rec.data_ptr(), projd.data_ptr(), ld, c_r, c_k, c_v, c_a, c_l, lora, dw[0].data_ptr(),
+                               dw[1].data_ptr(), dw[2].data_ptr(), T, heads, dim, math.exp(-0.5), 1e-6, cabi.PG_F32, st))
     segs, row = [], 0
     for s, n in zip(slot_of, lens):
         segs += [s, row, n]
         row += n
     segs += [0, 0, 0]                                # a padded empty segment leaves slot 0 alone
-    cabi.check(L.pg_delta_rule(o.data_ptr(), state.data_ptr(), projd.data_ptr(), ld, c_r, c_k, c_v, dec.data_ptr(),
-                               unit.data_ptr(), rem.data_ptr(), _i32(segs).data_ptr(), len(segs) // 3, heads, dim,
-                               cabi.PG_F32, st))
+    cabi.check(L.pg_delta_rule(o.data_ptr(), state.data_ptr(), rec.data_ptr(), _i32(segs).data_ptr(), len(segs) // 3, heads,
+                               dim, st))
     out = torch.zeros(T, nd + 8, device="cuda")
     cabi.check(L.pg_headnorm_gate(out.data_ptr(), nd + 8, o.data_ptr(), dw[3].data_ptr(), projd[:, c_g:].data_ptr(), ld, T,
                                   heads, dim, 1e-4, 1.3, cabi.PG_F32, st))
     p64 = proj.to(F64)
     w = torch.exp(-math.exp(-0.5) * O.sigmoid(O.lin(w2, torch.tanh(p64[:, c_l:c_l + lora])) + w0.to(F64)))
     a = O.sigmoid(p64[:, c_a:c_a + nd] + ab.to(F64))
-    _close(dec, w, 1e-6)
+    dp = (dim + 3) // 4 * 4
+    recs = rec.view(T, heads, 6, dp)                 # [r | k | w | u | a*u | v], padded columns zero
+    _close(recs[:, :, 2, :dim], w.reshape(T, heads, dim), 1e-6)
+    assert dp == dim or float(recs[..., dim:].abs().max()) == 0.0
     row = 0
     for s, n in zip(slot_of, lens):
         sl = slice(row, row + n)
