@@ -218,7 +218,7 @@ delta_rule_kernel(float* __restrict__ out, float* __restrict__ state, const floa
 template <typename T>
 __global__ void headnorm_gate_kernel(T* __restrict__ out, int ld_out, const float* __restrict__ o, const T* __restrict__ w,
                                      const T* __restrict__ gate, int ld_gate, int n_tokens, int heads, int dim, float eps,
-                                     float out_scale) {
+                                     float out_scale, int pairs) {
   pdl_launch_dependents();
   pdl_wait();
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -227,6 +227,28 @@ __global__ void headnorm_gate_kernel(T* __restrict__ out, int ld_out, const floa
   const int t = (int)(item / heads), h = (int)(item % heads);
   const float* orow = o + ((size_t)t * heads + h) * dim;
   float ss = 0.f;
+  if (pairs) {                                     // two columns per lane and access (even sizes, aligned rows)
+    for (int c = 2 * lane; c < dim; c += 64) { const float2 v = *reinterpret_cast<const float2*>(orow + c); ss += v.x * v.x + v.y * v.y; }
+    ss = warp_sum(ss);
+    const float inv = out_scale / sqrtf(ss / (float)dim + eps);
+    for (int c = 2 * lane; c < dim; c += 64) {
+      const float2 v = *reinterpret_cast<const float2*>(orow + c);
+      float a = v.x * inv, b = v.y * inv;
+      if (w) { a *= to_f<T>(w[h * dim + c]); b *= to_f<T>(w[h * dim + c + 1]); }
+      if (gate) {
+        const T* gp = gate + (size_t)t * ld_gate + h * dim + c;
+        a *= sigmoid_f(to_f<T>(gp[0])); b *= sigmoid_f(to_f<T>(gp[1]));
+      }
+      T* op = out + (size_t)t * ld_out + h * dim + c;
+      if constexpr (sizeof(T) == 2) {
+        T two[2] = {from_f<T>(a), from_f<T>(b)};
+        *reinterpret_cast<uint32_t*>(op) = *reinterpret_cast<const uint32_t*>(two);
+      } else {
+        op[0] = from_f<T>(a); op[1] = from_f<T>(b);
+      }
+    }
+    return;
+  }
   for (int c = lane; c < dim; c += 32) ss += orow[c] * orow[c];
   ss = warp_sum(ss);
   const float inv = 1.f / sqrtf(ss / (float)dim + eps);
@@ -289,10 +311,12 @@ extern "C" int pg_headnorm_gate(void* out, int ld_out, const float* o, const voi
   if (n_tokens <= 0) return PG_OK;
   PG_REQUIRE(out && o && heads > 0 && dim > 0, "headnorm_gate: bad arguments");
   const int warps = 8;
+  const int pairs = (dim % 2 == 0 && ld_out % 2 == 0 && ld_gate % 2 == 0 && ((uintptr_t)out % 4) == 0 &&
+                     ((uintptr_t)o % 8) == 0) ? 1 : 0;
   PG_DISPATCH_DTYPE(dtype, T, {
     return launch_pdl("headnorm_gate", headnorm_gate_kernel<T>, dim3(cdiv((long long)n_tokens * heads, warps)),
                       dim3(warps * 32), 0, (cudaStream_t)stream, (T*)out, ld_out, o, (const T*)w, (const T*)gate, ld_gate,
-                      n_tokens, heads, dim, eps, out_scale);
+                      n_tokens, heads, dim, eps, out_scale, pairs);
   });
   return PG_OK;
 }
