@@ -357,8 +357,18 @@ CONFIGS = {
         O.layer(O.parallel(heads=2, kv_heads=1, dim=128, vdim=64, scale=0.09, rot_dims=64, r_heads=2, r_dim=64), 64),
         O.layer(O.attn(heads=4, kv_heads=2, dim=64, vdim=128, rot_dims=32, scale=0.12, window=70, keep_first=66), 0),
         O.layer(O.parallel(heads=2, kv_heads=2, dim=64, vdim=64, scale=0.12, rot_dims=16, r_heads=1, r_dim=128), 32)]),
+    # nothing a multiple of anything: odd width, odd head sizes, one recurrent head of odd size, decay rank 1
+    "ragged_sizes": O.make_config(width=50, vocab=33, eps=1e-6, layers=[
+        O.layer(O.parallel(heads=5, kv_heads=5, dim=9, vdim=7, rot_dims=4, scaling=(2.0, 16, 3.0, 0.7), r_heads=1, r_dim=9,
+                           left_scale=1.7, right_scale=0.2), 19),
+        O.layer(O.attn(heads=5, kv_heads=1, dim=7, vdim=3, rot_dims=6, window=65, keep_first=64, v_mix=False), 0)]),
+    # a width at which the 16-bit run crosses the tensor-core GEMM kernels (fused projections, GeGLU epilogue, split-K)
+    "mid": O.make_config(width=384, vocab=600, layers=[
+        O.layer(O.attn(heads=6, kv_heads=2, dim=64, vdim=64, rot_dims=64, scale=0.12, window=80, keep_first=2), 1024),
+        O.layer(O.parallel(heads=6, kv_heads=3, dim=64, vdim=64, scale=0.1, rot_dims=32, r_heads=6, r_dim=64), 1024),
+        O.layer(O.attn(heads=6, kv_heads=2, dim=64, vdim=64, rot_dims=64, scale=0.12, window=80, keep_first=2), 1024)]),
 }
-LORA = {"small": 6, "parallel_first": 16, "odd": 3, "wide": 32}
+LORA = {"small": 6, "parallel_first": 16, "odd": 3, "wide": 32, "ragged_sizes": 1, "mid": 24}
 _ORACLE_CACHE = {}
 
 
