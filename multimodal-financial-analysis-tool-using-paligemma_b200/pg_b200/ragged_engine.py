@@ -151,9 +151,9 @@ class RaggedEngine(PagePool):
         T, nw = len(ids), len(want_rows)
         if T == 0:
             return torch.empty((0, self.cfg.vocab), dtype=torch.float32, device=self.device)
-        if self.max_positions is not None and max(positions) >= self.max_positions:
-            raise ValueError(f"position {max(positions)} exceeds max_positions {self.max_positions}")
         slots_np, pos_np = np.asarray(slots, dtype=np.int64), np.asarray(positions, dtype=np.int64)
+        if self.max_positions is not None and int(pos_np.max()) >= self.max_positions:
+            raise ValueError(f"position {int(pos_np.max())} exceeds max_positions {self.max_positions}")
         bounds = self._runs(slots_np, pos_np)
         segs: List[int] = []
         if self.needs_segments:
@@ -168,7 +168,7 @@ class RaggedEngine(PagePool):
                 for t0 in range(r0, r1, 128):
                     tiles += [t0, min(128, r1 - t0), int(slots_np[t0]), int(pos_np[t0])]
         nt = len(tiles) // 4
-        host = torch.empty(4 * T + nw + 3 * ns + 4 * nt, dtype=torch.int32).pin_memory()
+        host = torch.empty(4 * T + nw + 3 * ns + 4 * nt, dtype=torch.int32).pin_memory()   # torch caches pinned blocks
         host[:2 * T].view(torch.int64).copy_(torch.from_numpy(np.asarray(ids, dtype=np.int64)))
         host[2 * T:3 * T].copy_(torch.from_numpy(slots_np))
         host[3 * T:4 * T].copy_(torch.from_numpy(pos_np))

@@ -24,6 +24,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional
 
+import numpy as np
 import torch
 
 from .engine import PagedKV, PaliGemmaEngine
@@ -331,17 +332,25 @@ class RaggedBatcher:
     def run_entries(self, entries, layer_sink=None) -> torch.Tensor:
         """entries: (key, tokens, want) triples, `want` = indices into `tokens` whose logits are asked for.  All
         entries form ONE batch.  Returns fp32 logits, one row per wanted place, in entry order."""
-        ids, slots, positions, rows = [], [], [], []
+        ids, slots, positions, rows, base = [], [], [], [], 0
+        big = sum(len(e[1]) for e in entries) > 256       # prompt portions: arrays; a handful of tokens: plain lists
         for key, toks, want in entries:
             slot = self.slot_of[key]
-            n0 = self.kv.host_len[slot]
-            self.kv.ensure(slot, n0 + len(toks))
-            base = len(ids)
-            ids.extend(int(t) for t in toks)
-            slots.extend([slot] * len(toks))
-            positions.extend(range(n0, n0 + len(toks)))
+            n0, n = self.kv.host_len[slot], len(toks)
+            self.kv.ensure(slot, n0 + n)
+            if big:
+                ids.append(np.asarray(toks, dtype=np.int64))
+                slots.append(np.full(n, slot, dtype=np.int64))
+                positions.append(np.arange(n0, n0 + n, dtype=np.int64))
+            else:
+                ids.extend(int(t) for t in toks)
+                slots.extend([slot] * n)
+                positions.extend(range(n0, n0 + n))
             rows.extend(base + int(i) for i in want)
-            self.kv.host_len[slot] = n0 + len(toks)
+            base += n
+            self.kv.host_len[slot] = n0 + n
+        if big:
+            ids, slots, positions = (np.concatenate(x) for x in (ids, slots, positions))
         self.steps_run += 1
         return self.eng.forward_tokens(self.kv, ids, slots, positions, rows, layer_sink=layer_sink)
 
