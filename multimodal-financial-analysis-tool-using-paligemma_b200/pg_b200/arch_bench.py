@@ -369,9 +369,9 @@ def _decode_bytes(s: dict, cfg: dict, B: int) -> float:
 NINISUN_SIZES = {
     # attention layers: heads x dim over kv heads, window + kept first tokens, half of every head rotated, value mixing;
     # the parallel layer: the same head layout for the sigmoid attention, r_heads x r_dim recurrent heads, decay rank
-    "w1024": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, vdim=128, window=512, keep_first=4, ff=4096,
+    "w1024": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, vdim=128, window=512, keep_first=8, ff=4096,
                   r_heads=16, r_dim=64, lora=64, vocab=32000),
-    "w2048": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep_first=4, ff=8192,
+    "w2048": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep_first=8, ff=8192,
                   r_heads=32, r_dim=64, lora=64, vocab=32000),
 }
 
@@ -384,15 +384,15 @@ def ninisun_config(s: dict) -> dict:
         att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"],
                "scale": 1.0 / math.sqrt(s["dim"])}
         if i % 4 == 2:
-            left = dict(att, rot={"dims": s["dim"] // 2, "base": 500000.0,
-                                  "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}})
+            left = dict(att, rot={"dims": s["dim"] // 2, "base": 250000.0,
+                                  "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}})
             layers.append({"type": "parallel", "mlp": mlp, "mixer": {
-                "left": left, "right": {"heads": s["r_heads"], "dim": s["r_dim"]}, "left_scale": 0.8, "right_scale": 0.5}})
+                "left": left, "right": {"heads": s["r_heads"], "dim": s["r_dim"]}, "left_scale": 0.7, "right_scale": 0.6}})
         else:
             layers.append({"type": "attention", "mlp": mlp, "mixer": dict(
-                att, rot={"dims": s["dim"] // 2, "base": 1000000.0}, v_mix=True,
+                att, rot={"dims": s["dim"] // 2, "base": 10000.0}, v_mix=True,
                 mask={"size": s["window"], "keep_first": s["keep_first"]})})
-    return {"architecture": "Ninisun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "layers": layers}
+    return {"architecture": "Ninisun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "layers": layers}
 
 
 def random_ninisun_weights(cfg: dict, s: dict, device, dtype, seed=0) -> Dict[str, torch.Tensor]:

@@ -187,7 +187,7 @@ def _attention_case(H, G, dim, vdim, window, keep, lens, new, sigmoid, dtype=tor
             gt = torch.randn(n, H, generator=g)
             if dtype != torch.float32:
                 gt = gt.to(dtype).float()
-            o = o * O.sigmoid(gt.to(F64))[:, :, None] * 0.8
+            o = o * O.sigmoid(gt.to(F64))[:, :, None] * 0.65
             gate_rows.append(gt[n - m:])
         else:
             o = O.window_softmax_attention(q.to(F64), k.to(F64), v.to(F64), scale, window, keep)
@@ -214,7 +214,7 @@ def _attention_case(H, G, dim, vdim, window, keep, lens, new, sigmoid, dtype=tor
             out.data_ptr(), H * vdim + 8, q_all.data_ptr(), H * dim, None if gate is None else gate.data_ptr(), H,
             1 if sigmoid else 0, pg.k.data_ptr(), pg.v.data_ptr(), pg.k.shape[0] * PAGE, pg.table.data_ptr(), pg.max_pages,
             PAGE, _i32(tiles).data_ptr(), len(tiles) // 4, T, H, G, dim, vdim, scale, window, keep, None,
-            1 if sigmoid else 0, pbd.data_ptr() if sigmoid else None, 0.8 if sigmoid else 1.0, err.data_ptr(), CT[dtype], st))
+            1 if sigmoid else 0, pbd.data_ptr() if sigmoid else None, 0.65 if sigmoid else 1.0, err.data_ptr(), CT[dtype], st))
         torch.cuda.synchronize()
         assert int(err) == 0
         return out[:, :H * vdim].float(), torch.cat(want)
@@ -222,21 +222,21 @@ def _attention_case(H, G, dim, vdim, window, keep, lens, new, sigmoid, dtype=tor
         out.data_ptr(), H * vdim + 8, q_all.data_ptr(), H * dim, None if gate is None else gate.data_ptr(), H,
         1 if sigmoid else 0, pg.k.data_ptr(), pg.v.data_ptr(), pg.table.data_ptr(), pg.max_pages, PAGE,
         _i32(slots).data_ptr(), _i32(positions).data_ptr(), T, H, G, dim, vdim, scale, window, keep, None,
-        1 if sigmoid else 0, pbd.data_ptr() if sigmoid else None, 0.8 if sigmoid else 1.0, ws.data_ptr(), ws.numel(),
+        1 if sigmoid else 0, pbd.data_ptr() if sigmoid else None, 0.65 if sigmoid else 1.0, ws.data_ptr(), ws.numel(),
         CT[dtype], st))
     torch.cuda.synchronize()
     return out[:, :H * vdim].float(), torch.cat(want)
 
 
-@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 8, 16), (6, 1, 12, 20), (2, 2, 64, 32), (8, 2, 32, 48), (8, 1, 16, 128)])
-@pytest.mark.parametrize("window,keep", [(0, 0), (5, 0), (5, 3), (3, 7), (64, 4), (72, 4), (130, 70), (1, 1)])
+@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 8, 16), (6, 1, 12, 20), (2, 2, 64, 32), (8, 2, 32, 40), (8, 1, 16, 128)])
+@pytest.mark.parametrize("window,keep", [(0, 0), (5, 0), (5, 3), (3, 7), (64, 4), (75, 5), (130, 70), (1, 1)])
 def test_windowed_attention_with_kept_first_tokens(H, G, dim, vdim, window, keep):
     # prompt portions that start in the middle of a page and single decoded tokens far into their sequences
     got, want = _attention_case(H, G, dim, vdim, window, keep, lens=[150, 1, 201, 66], new=[40, 1, 1, 2], sigmoid=False)
     _rows_close(got, want, 2e-5)
 
 
-@pytest.mark.parametrize("window,keep", [(5, 3), (72, 4), (100, 64), (70, 0)])
+@pytest.mark.parametrize("window,keep", [(5, 3), (75, 5), (100, 64), (70, 0)])
 @pytest.mark.parametrize("where", ["window_in", "window_out", "first_in", "first_out"])
 @pytest.mark.parametrize("decode", [True, False])
 def test_a_towering_key_at_every_edge(window, keep, where, decode):
@@ -271,7 +271,7 @@ def test_tensor_core_attention_portions_windows_kept_tokens(H, G, dim, vdim, win
     _rows_close(got, want, 2e-2)
 
 
-@pytest.mark.parametrize("window,keep", [(72, 4), (100, 64), (70, 0), (130, 65)])
+@pytest.mark.parametrize("window,keep", [(75, 5), (100, 64), (70, 0), (130, 65)])
 @pytest.mark.parametrize("where", ["window_in", "window_out", "first_in", "first_out"])
 def test_tensor_core_attention_towering_key_at_every_edge(window, keep, where):
     tower = {"window_in": lambda i: i - window + 1, "window_out": lambda i: i - window,
@@ -282,7 +282,7 @@ def test_tensor_core_attention_towering_key_at_every_edge(window, keep, where):
         _rows_close(got, want, 2e-2)
 
 
-@pytest.mark.parametrize("heads,dim,lora", [(3, 8, 6), (1, 48, 16), (2, 64, 5), (2, 100, 8), (1, 130, 4)])
+@pytest.mark.parametrize("heads,dim,lora", [(3, 8, 6), (1, 44, 12), (2, 64, 5), (2, 100, 8), (1, 130, 4)])
 def test_delta_rule_prep_recurrence_head_norm(heads, dim, lora):
     cabi, L, st = _lib()
     g = torch.Generator().manual_seed(11)

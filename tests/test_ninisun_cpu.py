@@ -46,7 +46,7 @@ def test_config_rejects_what_the_design_does_not_have():
         NinisunConfig.from_dict(bad)
 
 
-@pytest.mark.parametrize("dims,base,scaling", [(8, 10000.0, None), (16, 500000.0, (4.0, 1024, 32.0, 1.0)),
+@pytest.mark.parametrize("dims,base,scaling", [(8, 10000.0, None), (16, 300000.0, (3.0, 2048, 24.0, 2.0)),
                                                (6, 77.0, (2.5, 100, 8.0, 0.5)), (32, 1e6, (8.0, 4096, 1.0, 1.0))])
 def test_rotary_table_matches_the_oracle(dims, base, scaling):
     f, mag = RotaryCfg(dims, base, dict(zip(("factor", "original", "fast", "slow"), scaling)) if scaling else None).table()
