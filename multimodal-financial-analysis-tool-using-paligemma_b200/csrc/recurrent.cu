@@ -134,7 +134,7 @@ delta_rule_kernel(float* __restrict__ out, float* __restrict__ state, const floa
   const int32_t* sg = segs + 3 * (size_t)blockIdx.x;
   const int slot = sg[0], row0 = sg[1], n = sg[2];
   if (n <= 0) return;
-  const int h = blockIdx.y, j = threadIdx.x / RG, rg = threadIdx.x % RG, nd = heads * dim;
+  const int h = blockIdx.y, j = blockIdx.z * (blockDim.x / RG) + threadIdx.x / RG, rg = threadIdx.x % RG, nd = heads * dim;
   const bool live = j < dim;
   constexpr int RSZ = REC_VECS * DMAX;              // floats of one record in shared memory
   if (dp < DMAX)
@@ -265,8 +265,13 @@ static int launch_delta(float* out, float* state, const float* rec, const int32_
                         cudaStream_t st) {
   const int dp = (dim + 3) / 4 * 4;
   const size_t smem = sizeof(float) * 2 * CH * REC_VECS * DMAX;
-  return launch_pdl("delta_rule", delta_rule_kernel<DMAX, CH>, dim3(n_segs, heads), dim3(DMAX * 4), smem, st, out, state, rec, segs,
-                    heads, dim, dp);
+  // few (segment, head) pairs: the value columns of a head are cut over `cut` CTAs (each fetches the head's records)
+  static const int cut_env = env_int("PG_DELTA_COLUMN_CUT", 0);
+  int cut = 1;
+  if (DMAX >= 16 && (long long)n_segs * heads * 2 <= 160) cut = 2;   // measured: 0.95 -> 0.68 ms at 64 pairs, slower from 128 on
+  if (cut_env > 0 && DMAX / cut_env >= 8) cut = cut_env;
+  return launch_pdl("delta_rule", delta_rule_kernel<DMAX, CH>, dim3(n_segs, heads, cut), dim3(DMAX * 4 / cut), smem, st, out, state,
+                    rec, segs, heads, dim, dp);
 }
 
 }  // namespace pg

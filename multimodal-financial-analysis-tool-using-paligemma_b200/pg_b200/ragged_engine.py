@@ -11,8 +11,8 @@ Inputs of a step on the device (one int32 buffer, `StepInputs` names its parts):
     ids (int64) | page-table row | position | wanted rows | segments | query tiles
 
 * segments (engines with `needs_segments`: recurrent state per sequence slot): {slot, first token row, tokens} for
-  every run of consecutive tokens of one sequence, padded with empty segments to min(tokens, slots) entries so that a
-  captured launch sequence depends on the token count only;
+  every run of consecutive tokens of one sequence; steps that replay a graph pad the list with empty segments to
+  min(tokens, slots) entries so that the captured launch sequence depends on the token count only;
 * query tiles (steps of at least `attn_tc_min_tokens` tokens on engines whose attention has a tensor-core kernel):
   {first token row, rows, page-table row, first position} for runs of up to 128 consecutive tokens of one sequence.
 """
@@ -156,10 +156,12 @@ class RaggedEngine(PagePool):
             raise ValueError(f"position {int(pos_np.max())} exceeds max_positions {self.max_positions}")
         bounds = self._runs(slots_np, pos_np)
         segs: List[int] = []
+        replay = (T <= self.graph_max_tokens and layer_sink is None and not self._op_timing
+                  and not torch.cuda.is_current_stream_capturing())
         if self.needs_segments:
             segs = self._segments(slots_np, bounds)
-            n_max = min(T, int(kv.page_table.shape[0]))
-            segs += [0, 0, 0] * (n_max - len(segs) // 3)
+            if replay:      # a captured launch sequence must depend on the token count only: pad with empty segments
+                segs += [0, 0, 0] * (min(T, int(kv.page_table.shape[0])) - len(segs) // 3)
         ns = len(segs) // 3
         # query tiles of the tensor-core attention: runs of <= 128 consecutive tokens of one sequence
         tiles: List[int] = []
@@ -178,8 +180,7 @@ class RaggedEngine(PagePool):
             host[4 * T + nw:4 * T + nw + 3 * ns].copy_(torch.as_tensor(segs, dtype=torch.int32))
         if nt:
             host[4 * T + nw + 3 * ns:].copy_(torch.as_tensor(tiles, dtype=torch.int32))
-        if (T <= self.graph_max_tokens and layer_sink is None and not self._op_timing and nt == 0
-                and not torch.cuda.is_current_stream_capturing()):
+        if replay and nt == 0:
             return self._replay(kv, host, T, nw, ns)
         return self._forward_device(kv, self._inputs(host.to(self.device, non_blocking=True), T, nw, ns), layer_sink)
 

@@ -492,6 +492,16 @@ def test_greedy_generation_through_the_scheduler():
         assert done[rid].tokens == seq[len(p):]
     b.close()
     assert eng.pages_in_use() == 0
+    # the framework's top-p kernel on the same scheduler: tokens of the vocabulary, the same seed gives the same tokens
+    runs = []
+    for _ in range(2):
+        b = eng.new_batcher(slots=2, token_budget=32, do_sample=True, temperature=0.9, top_p=0.8, seed=5)
+        rids = [b.submit(p, max_new_tokens=5) for p in prompts[:2]]
+        done = b.run()
+        runs.append([done[r].tokens for r in rids])
+        b.close()
+    assert runs[0] == runs[1] and all(0 <= t < cfg["vocab"] for seq in runs[0] for t in seq)
+    assert all(len(seq) == 5 for seq in runs[0])
 
 
 def test_model_folder_through_the_registry(tmp_path):
