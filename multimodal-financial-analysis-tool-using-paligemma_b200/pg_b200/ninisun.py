@@ -31,6 +31,7 @@ are the framework's (`ragged_engine.RaggedEngine`, `scheduler.SlotKV` / `SlotSta
 from __future__ import annotations
 
 import math
+import warnings
 from dataclasses import dataclass, field
 from typing import Dict, List, Mapping, Optional
 
@@ -171,8 +172,9 @@ class NinisunEngine(RaggedEngine):
     """Weights + paged pools + recurrent state shapes + the launch sequence of one step over a ragged token batch."""
 
     def __init__(self, config, weights: Mapping[str, torch.Tensor], *, device="cuda", dtype=torch.bfloat16,
-                 page_size: int = 64, kv_pool_tokens: int = 65536, gemm_impl: int = 0):
+                 page_size: int = 64, kv_pool_tokens: int = 65536, gemm_impl: int = 0, strict: bool = False):
         self.cfg = config if isinstance(config, NinisunConfig) else NinisunConfig.from_dict(config)
+        self.strict = bool(strict)      # True: tensors the config does not call for raise instead of being reported
         self._init_common(device=device, dtype=dtype, page_size=page_size, gemm_impl=gemm_impl)
         self.needs_segments = any(L.delta is not None for L in self.cfg.layers)
         self._repack(weights)
@@ -223,11 +225,14 @@ class NinisunEngine(RaggedEngine):
                 w["o"], w["att_cols"] = W(m + "o", (D, ng)), ng
                 w["lam"], w["mix_from"] = 0.0, None
                 if a.v_mix:
-                    lam = float(W(m + "vmix", (), torch.float32))
                     if first_mix is None:
                         first_mix = i                 # the first such layer gives its values, its own weight is unused
+                        used.add(m + "vmix")
                     else:
-                        w["lam"], w["mix_from"] = lam, first_mix
+                        lam = W(m + "vmix", None, torch.float32)
+                        if lam.numel() != 1:
+                            raise ValueError(f"tensor {m}vmix: one mixing weight expected, shape {tuple(lam.shape)}")
+                        w["lam"], w["mix_from"] = float(lam.reshape(())), first_mix
             else:
                 l, r, d = p + "mix.left.", p + "mix.right.", L.delta
                 nd = d.heads * d.dim
@@ -256,7 +261,10 @@ class NinisunEngine(RaggedEngine):
             self.layers.append(w)
         extra = sorted(set(weights) - used)
         if extra:
-            raise ValueError(f"checkpoint holds {len(extra)} tensor(s) the config does not describe: {extra[:5]}")
+            text = f"checkpoint holds {len(extra)} tensor(s) the config does not call for: {extra[:8]}"
+            if self.strict:
+                raise ValueError(text)
+            warnings.warn(text + " (not used)")
 
     # ------------------------------------------------------------------ recurrent state
     def new_slot_state(self, slots: int):

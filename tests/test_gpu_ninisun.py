@@ -519,7 +519,16 @@ def test_model_folder_through_the_registry(tmp_path):
     b.admit(0)
     _rows_close(b.run_entries([(0, toks, [39, 0])]), O.forward(cfg, ck, toks)[[39, 0]], 1e-4)
     b.close()
-    bad = dict(ck)
-    bad["l0.mix.extra"] = torch.zeros(3)
+    more = dict(ck)
+    more["l0.mix.extra"] = torch.zeros(3)                  # a tensor the config does not call for: reported, or refused
+    with pytest.warns(UserWarning):
+        type(eng)(cfg, more, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64)
     with pytest.raises(ValueError):
-        type(eng)(cfg, bad, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64)
+        type(eng)(cfg, more, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64, strict=True)
+    less = {k: v for k, v in ck.items() if k != "l1.mix.q"}
+    with pytest.raises(KeyError):
+        type(eng)(cfg, less, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64)
+    wrong = dict(ck)
+    wrong["l1.mix.q"] = torch.zeros(5, cfg["width"])
+    with pytest.raises(ValueError):
+        type(eng)(cfg, wrong, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64)
