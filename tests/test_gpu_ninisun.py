@@ -532,3 +532,50 @@ def test_model_folder_through_the_registry(tmp_path):
     wrong["l1.mix.q"] = torch.zeros(5, cfg["width"])
     with pytest.raises(ValueError):
         type(eng)(cfg, wrong, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64)
+
+
+def test_command_line_replay_and_generation(tmp_path):
+    """bin/trace_run replays a schedule (portions beside single tokens, a slot handed on) and bin/generate generates,
+    both on a model folder picked up through the registry."""
+    import subprocess
+    import sys
+    import numpy as np
+    from pg_b200.checkpoint import write_safetensors
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = CONFIGS["small"]
+    ck = O.make_checkpoint(cfg, 0, lora=LORA["small"])
+    model = tmp_path / "model"
+    model.mkdir()
+    with open(model / "config.json", "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(str(model / "model.safetensors"), ck)
+    seq = {k: _tokens(n, cfg["vocab"], 60 + n) for k, n in (("a", 22), ("b", 5), ("c", 70))}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": seq["a"][:20], "want": [19]}, {"id": "b", "tokens": seq["b"], "want": [0, 4]}],
+         "end": ["b"]},
+        {"step": 1, "entries": [{"id": "a", "tokens": seq["a"][20:21], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "c", "tokens": seq["c"], "want": [69]}, {"id": "a", "tokens": seq["a"][21:], "want": [0]}],
+         "end": ["a", "c"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model), "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not (out / "1.f32").exists()                      # nothing was asked for in step 1
+    ref = {k: O.forward(cfg, ck, v) for k, v in seq.items()}
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(3, cfg["vocab"]))
+    _rows_close(got0, torch.stack([ref["a"][19], ref["b"][0], ref["b"][4]]), 1e-4)
+    got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, cfg["vocab"]))
+    _rows_close(got2, torch.stack([ref["c"][69], ref["a"][21]]), 1e-4)
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "generate"), "--model", str(model), "--dtype", "float32",
+                        "--prompt-ids", ",".join(map(str, seq["b"])), "--prompt-ids", ",".join(map(str, seq["a"])),
+                        "--max-new-tokens", "4", "--max-tokens", "256", "--slots", "2"], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(ln) for ln in r.stdout.splitlines() if ln.startswith("{")]
+    for i, key in enumerate(("b", "a")):
+        s = list(seq[key])
+        for _ in range(4):
+            s.append(int(O.forward(cfg, ck, s)[-1].argmax()))
+        assert lines[i] == {"request": i, "tokens": s[len(seq[key]):]}
